@@ -1,0 +1,187 @@
+/*
+ * b200attn — C ABI of the B200 (sm_100a) attention + paged KV-cache kernels.
+ *
+ * This library stands where tt-xla's vLLM plugin lowers its attention custom ops
+ * through PJRT and TT-MLIR.  Every entry point replaces the device side of one
+ * `torch.ops.tt.*` op (python_package/tt_torch/custom_ops.py) as it is called from
+ * integrations/vllm_plugin/vllm_tt/attention_impls/attention.py; the citation
+ * above each declaration names the reference interface it replaces.
+ *
+ * Conventions
+ *   - All pointers are CUDA device pointers unless a parameter says "host".
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *     Every call is asynchronous on that stream.
+ *   - Return value: 0 = launched; negative = argument rejected on the host, nothing
+ *     was launched; positive = a cudaError_t from the launch.  Nothing throws,
+ *     aborts or traps.  There is no CPU fallback: without a CUDA device every
+ *     compute entry point returns B200ATTN_ERR_NO_DEVICE.
+ *   - The library allocates no device memory; split-KV scratch is passed in by the
+ *     caller (see b200attn_decode_workspace_bytes).
+ *   - K/V cache layout is the plugin's: one K and one V tensor per layer, each
+ *     [num_blocks, num_kv_heads, block_size, head_size] contiguous
+ *     (attention.py:103-112).  Element (blk,h,off,d) sits at
+ *     ((blk*num_kv_heads + h)*block_size + off)*head_size + d.
+ *   - Head counts are the LOCAL (per tensor-parallel rank) counts.
+ *   - Supported: bf16 data, head_size in {64,128}, block_size in {32,64},
+ *     num_q_heads/num_kv_heads <= 16 for decode.  Anything else is rejected with
+ *     B200ATTN_ERR_UNSUPPORTED.
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200ATTN_VERSION 100
+
+enum b200attn_status {
+  B200ATTN_OK = 0,
+  B200ATTN_ERR_NULL_POINTER = -1,
+  B200ATTN_ERR_UNSUPPORTED = -2,   /* head_size / block_size / group size outside the supported set */
+  B200ATTN_ERR_MISALIGNED = -3,    /* a pointer or stride breaks the 16-byte rule */
+  B200ATTN_ERR_WORKSPACE = -4,     /* workspace missing or too small */
+  B200ATTN_ERR_BAD_ARGUMENT = -5,  /* negative sizes, inconsistent head counts ... */
+  B200ATTN_ERR_NO_DEVICE = -6,     /* no CUDA device / driver entry point unavailable */
+  B200ATTN_ERR_TENSOR_MAP = -7,    /* cuTensorMapEncodeTiled refused the layout */
+  B200ATTN_ERR_TOO_LARGE = -8      /* size beyond a documented maximum */
+};
+
+/* Device-side diagnostics word values (see b200attn_read_error_word). */
+enum b200attn_device_error {
+  B200ATTN_DEV_OK = 0,
+  B200ATTN_DEV_WAIT_TIMEOUT = 1,   /* a bounded mbarrier wait ran out */
+  B200ATTN_DEV_BAD_INDEX = 2       /* a page id or slot was outside the cache */
+};
+
+/* Library version (B200ATTN_VERSION of the build). */
+int b200attn_version(void);
+
+/* Human-readable text for a status returned by any entry point. */
+const char* b200attn_status_string(int status);
+
+/* ------------------------------------------------------------------------------------------
+ * KV-cache write, decode form.
+ * Replaces: torch.ops.tt.paged_update_cache called once for K and once for V
+ *           (custom_ops.py:962-1013; call site attention.py:468-484).
+ * For every user u: pos = update_indices[u];
+ *   cache[page_table[u, pos / block_size], :, pos % block_size, :] = new[u, :, :]
+ * with Python floor-division / modulo and negative-index wrap-around on the page-table
+ * column, exactly as the reference's CPU branch indexes (custom_ops.py:985-998).
+ * k_new / v_new are token-major: element (u,h,d) at u*new_token_stride + h*head_size + d.
+ * The caches are updated in place (the reference returns a clone and copies it back,
+ * attention.py:513-515; the observable result is the same).
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_paged_update_cache(void* k_cache, void* v_cache,
+                                const void* k_new, const void* v_new,
+                                int64_t new_token_stride,
+                                const int32_t* update_indices,
+                                const int32_t* page_table, int64_t page_table_stride,
+                                int page_table_width,
+                                int num_users, int num_kv_heads, int head_size,
+                                int block_size, int64_t num_blocks, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * KV-cache write, prefill / chunk form.
+ * Replaces: torch.ops.tt.paged_fill_cache called once for K and once for V
+ *           (custom_ops.py:1016-1104; call site attention.py:485-511).
+ * User u's tokens_per_user tokens go to blocks fill_page_table[batch_idx[u], 0..),
+ * token t at block column t / block_size, offset t % block_size.  batch_idx may be NULL
+ * (= identity).  The reference's CPU branch serves one user per call
+ * (custom_ops.py:1044); this entry point serves all users of the batch at once, which is
+ * what the device op does.
+ * k_new / v_new are token-major with user u's token t at row u*tokens_per_user + t.
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_paged_fill_cache(void* k_cache, void* v_cache,
+                              const void* k_new, const void* v_new,
+                              int64_t new_token_stride,
+                              const int32_t* fill_page_table, int64_t page_table_stride,
+                              int page_table_width, const int32_t* batch_idx,
+                              int num_users, int tokens_per_user,
+                              int num_kv_heads, int head_size,
+                              int block_size, int64_t num_blocks, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * KV-cache write, slot-mapping form (what vLLM's own runners supply).
+ * Replaces: write_to_kv_cache(key, value, kv_cache, slot_mapping, ...)
+ *           (attention.py:671-716), re-targeted at the live cache layout above.
+ * Token t goes to block slot_mapping[t] / block_size, offset slot_mapping[t] % block_size;
+ * tokens with a negative slot are skipped (vLLM's padding convention).
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_kv_scatter_slots(void* k_cache, void* v_cache,
+                              const void* k_new, const void* v_new,
+                              int64_t new_token_stride,
+                              const int64_t* slot_mapping, int num_tokens,
+                              int num_kv_heads, int head_size,
+                              int block_size, int64_t num_blocks, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Paged GQA decode attention (one query token per user), split-KV + combine.
+ * Replaces: torch.ops.tt.paged_scaled_dot_product_attention_decode with is_causal=True and
+ *           cur_pos_tensor (custom_ops.py:1198-1331; call site attention.py:634-668).
+ * out[u,h,:] = softmax_{j <= cur_pos[u]}(q[u,h,:] . K_u[j, h/G, :] * scale) . V_u[j, h/G, :]
+ * where K_u/V_u are read through page_table[u, j / block_size].  Users with cur_pos < 0
+ * (padding rows) get zeros.  q and out are [num_users, num_q_heads, head_size] with the
+ * given row strides (elements).
+ * num_splits: 0 = choose (b200attn_decode_auto_splits with max_context_len); the workspace
+ * must hold b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits)
+ * bytes (it may be NULL when the split count in effect is 1).
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_paged_decode(void* out, int64_t out_row_stride,
+                          const void* q, int64_t q_row_stride,
+                          const void* k_cache, const void* v_cache,
+                          const int32_t* page_table, int64_t page_table_stride,
+                          int page_table_width, const int32_t* cur_pos,
+                          int num_users, int num_q_heads, int num_kv_heads, int head_size,
+                          int block_size, int64_t num_blocks, float scale,
+                          int max_context_len, int num_splits,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Split count the library would pick for a decode batch (host heuristic, no device access
+ * beyond the SM count).  max_context_len <= 0 means "unknown": the page-table width bounds it. */
+int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int block_size,
+                                int max_context_len);
+
+/* Bytes of scratch b200attn_paged_decode needs for num_splits splits (0 when num_splits <= 1). */
+size_t b200attn_decode_workspace_bytes(int num_users, int num_q_heads, int head_size,
+                                       int num_splits);
+
+/* ------------------------------------------------------------------------------------------
+ * Causal varlen prefill / chunked-prefill attention on tcgen05 tensor cores.
+ * Replaces: torch.ops.tt.scaled_dot_product_attention with is_causal=True, attn_mask=None
+ *           (custom_ops.py:635-742; call site attention.py:575-598)            [kv_is_paged = 0]
+ *      and: torch.ops.tt.chunked_scaled_dot_product_attention
+ *           (custom_ops.py:1334-1443; call site attention.py:545-560)          [kv_is_paged = 1]
+ * Sequence s owns query rows cu_q[s] .. cu_q[s+1]-1 of q/out (row strides in elements);
+ * query row i of the sequence sits at absolute position q_start[s] + i and attends keys
+ * 0 .. q_start[s] + i.  q_start may be NULL (= 0 for every sequence).  The reference passes
+ * one chunk_start for the whole batch; per-sequence starts are a superset.
+ *   kv_is_paged = 0: k_src / v_src are the fresh token-major K/V of the same tokens
+ *                    (row t at t*kv_token_stride, head h at h*head_size); q_start must be
+ *                    NULL or all zero; page_table is ignored.
+ *   kv_is_paged = 1: k_src / v_src are the K and V caches; page_table[s, :] lists sequence
+ *                    s's blocks in logical order (prefix + chunk already written).
+ * cu_q_host mirrors cu_q on the host (the launch grid is sized from it).
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_prefill(void* out, int64_t out_row_stride,
+                     const void* q, int64_t q_row_stride,
+                     const void* k_src, const void* v_src, int kv_is_paged,
+                     int64_t kv_token_stride,
+                     const int32_t* page_table, int64_t page_table_stride, int page_table_width,
+                     const int32_t* cu_q, const int32_t* cu_q_host,
+                     const int32_t* q_start,
+                     int num_seqs, int total_q, int num_q_heads, int num_kv_heads,
+                     int head_size, int block_size, int64_t num_blocks, float scale,
+                     void* stream);
+
+/* Copies the device diagnostics word of the current device to *out_host (synchronises the
+ * stream) and clears it.  0 = no kernel reported a problem since the last read. */
+int b200attn_read_error_word(int32_t* out_host, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H_ */

@@ -1,0 +1,150 @@
+"""Causal / chunked prefill kernel (tcgen05) against the oracle and the reference golden vectors
+(bf16 tolerance: max abs <= 2e-2, mean abs <= 2e-3 against fp32 arithmetic)."""
+import pytest
+import torch
+
+from oracle import restate
+from oracle.inputs import make_prefill_case, randn_bf16
+from tests.conftest import assert_attention_close
+from tests.golden.golden_io import load_case
+
+pytestmark = pytest.mark.gpu
+
+
+def cu(users, T):
+    return torch.arange(users + 1, dtype=torch.int32) * T
+
+
+def test_sdpa_golden(clean_error_word):
+    from b200attn import ops
+
+    c = load_case("sdpa_gqa")
+    B, nq, T, hd = c["q"].shape
+    nkv = c["k"].shape[1]
+    q = c["q"].transpose(1, 2).reshape(B * T, nq, hd).contiguous().cuda()
+    k = c["k"].transpose(1, 2).reshape(B * T, nkv, hd).contiguous().cuda()
+    v = c["v"].transpose(1, 2).reshape(B * T, nkv, hd).contiguous().cuda()
+    out = ops.prefill(q, k, v, cu(B, T), scale=float(c["scale"]))
+    got = out.reshape(B, T, nq, hd).transpose(1, 2)
+    assert_attention_close(got, c["out_fp32"], "sdpa golden")
+
+
+@pytest.mark.parametrize("start", [0, 64, 96])
+def test_chunked_golden(start, clean_error_word):
+    from b200attn import ops
+
+    c = load_case(f"chunked_start{start}")
+    users, nq, T, hd = c["q"].shape
+    q = c["q"].transpose(1, 2).reshape(users * T, nq, hd).contiguous().cuda()
+    out = ops.prefill(
+        q, c["k_cache"].cuda(), c["v_cache"].cuda(), cu(users, T), scale=float(c["scale"]),
+        page_table=c["page_table"].cuda(),
+        q_start=torch.full((users,), start, dtype=torch.int32, device="cuda"),
+    )
+    got = out.reshape(users, T, nq, hd).transpose(1, 2)
+    assert_attention_close(got, c["out_fp32"], f"chunked golden start={start}")
+
+
+# reference CPU test parametrisation (tests/torch/ops/test_chunked_sdpa_op_cpu.py): MHA, GQA 8/2
+# and 32/8, chunk_start 0 / 64 / 96, plus the supported larger geometries
+@pytest.mark.parametrize("nq,nkv", [(4, 4), (8, 2), (32, 8)])
+@pytest.mark.parametrize("hd,bs", [(64, 32), (128, 64)])
+@pytest.mark.parametrize("T,start", [(64, 0), (64, 64), (32, 96), (256, 0), (192, 320)])
+def test_chunked_vs_oracle(nq, nkv, hd, bs, T, start, clean_error_word):
+    from b200attn import ops
+
+    if start % bs:
+        pytest.skip("chunks start on a block boundary")
+    case = make_prefill_case(nq=nq, nkv=nkv, hd=hd, bs=bs, users=2, T=T, chunk_start=start,
+                             seed=nq * 3 + T + start)
+    # write the chunk's K/V into the cache on the CPU with the oracle, then attend on the GPU
+    k = case.k.reshape(2, T, nkv, hd)
+    v = case.v.reshape(2, T, nkv, hd)
+    kc = restate.paged_fill_cache(case.k_cache, k.transpose(1, 2), case.fill_page_table)
+    vc = restate.paged_fill_cache(case.v_cache, v.transpose(1, 2), case.fill_page_table)
+    q4 = case.q.reshape(2, T, nq, hd)
+    want = restate.chunked_sdpa(q4.transpose(1, 2).float(), kc.float(), vc.float(),
+                                case.page_table, start, case.scale).transpose(1, 2)
+    out = ops.prefill(
+        case.q.reshape(2 * T, nq, hd).cuda(), kc.cuda(), vc.cuda(), cu(2, T), scale=case.scale,
+        page_table=case.page_table.cuda(),
+        q_start=torch.full((2,), start, dtype=torch.int32, device="cuda"),
+    )
+    assert_attention_close(out.reshape(2, T, nq, hd), want, "chunked vs oracle")
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("T", [32, 128, 160, 512])
+def test_fresh_kv_causal_vs_oracle(hd, T, clean_error_word):
+    from b200attn import ops
+
+    g = torch.Generator().manual_seed(T + hd)
+    B, nq, nkv = 3, 8, 2
+    q = randn_bf16((B, T, nq, hd), g)
+    k = randn_bf16((B, T, nkv, hd), g)
+    v = randn_bf16((B, T, nkv, hd), g)
+    want = restate.sdpa(q.transpose(1, 2).float(), k.transpose(1, 2).float(),
+                        v.transpose(1, 2).float(), True, hd ** -0.5).transpose(1, 2)
+    out = ops.prefill(q.reshape(B * T, nq, hd).cuda(), k.reshape(B * T, nkv, hd).cuda(),
+                      v.reshape(B * T, nkv, hd).cuda(), cu(B, T), scale=hd ** -0.5)
+    assert_attention_close(out.reshape(B, T, nq, hd), want, "fresh causal")
+
+
+def test_varlen_ragged_lengths_and_starts(clean_error_word):
+    """Sequences of different query lengths and different prefix lengths in one call (a superset
+    of the reference's single shared chunk_start): each sequence equals its own oracle call."""
+    from b200attn import ops
+
+    g = torch.Generator().manual_seed(77)
+    nq, nkv, hd, bs = 8, 2, 128, 64
+    q_lens = [1, 37, 128, 200]
+    starts = [300, 64, 0, 128]
+    nblks = [(s + t + bs - 1) // bs for s, t in zip(starts, q_lens)]
+    width = max(nblks)
+    nb = sum(nblks) + 1
+    perm = torch.randperm(nb - 1, generator=g) + 1
+    pt = torch.zeros(len(q_lens), width, dtype=torch.int32)
+    o = 0
+    for i, n in enumerate(nblks):
+        pt[i, :n] = perm[o:o + n].int()
+        o += n
+    kc = randn_bf16((nb, nkv, bs, hd), g)
+    vc = randn_bf16((nb, nkv, bs, hd), g)
+    total = sum(q_lens)
+    q = randn_bf16((total, nq, hd), g)
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    out = ops.prefill(q.cuda(), kc.cuda(), vc.cuda(), cu_q, scale=hd ** -0.5,
+                      page_table=pt.cuda(),
+                      q_start=torch.tensor(starts, dtype=torch.int32).cuda()).cpu()
+    for i, (t, s) in enumerate(zip(q_lens, starts)):
+        qi = q[cu_q[i]:cu_q[i + 1]].transpose(0, 1)[None].float()      # [1,nq,t,hd]
+        want = restate.chunked_sdpa(qi, kc.float(), vc.float(), pt[i:i + 1, :nblks[i]], s,
+                                    hd ** -0.5)[0].transpose(0, 1)
+        assert_attention_close(out[cu_q[i]:cu_q[i + 1]], want, f"seq {i}")
+
+
+def test_paged_and_fresh_forms_agree_at_config2_shape(clean_error_word):
+    """BASELINE config 2 geometry (nq 32, nkv 8, hd 128, bs 64, T 2048) on one sequence: the
+    paged form with chunk_start 0 and the fresh-KV form give the same bits, and rows are
+    checked against the oracle on a strided subset of heads."""
+    from b200attn import ops
+
+    case = make_prefill_case(nq=32, nkv=8, hd=128, bs=64, users=1, T=2048, seed=2)
+    T, nq, nkv, hd = case.T, case.nq, case.nkv, case.hd
+    q = case.q.reshape(T, nq, hd).cuda()
+    k = case.k.reshape(T, nkv, hd).cuda()
+    v = case.v.reshape(T, nkv, hd).cuda()
+    kc, vc = case.k_cache.cuda(), case.v_cache.cuda()
+    ops.paged_fill_cache(kc, vc, k[None], v[None], case.fill_page_table.cuda())
+    fresh = ops.prefill(q, k, v, cu(1, T), scale=case.scale)
+    paged = ops.prefill(q, kc, vc, cu(1, T), scale=case.scale, page_table=case.page_table.cuda(),
+                        q_start=torch.zeros(1, dtype=torch.int32, device="cuda"))
+    assert torch.equal(fresh, paged)
+    heads = [0, 5, 31]
+    kv_heads = [h // (nq // nkv) for h in heads]
+    qh = case.q.reshape(T, nq, hd)[:, heads].transpose(0, 1)[None].float()
+    for i, (h, kh) in enumerate(zip(heads, kv_heads)):
+        want = restate.sdpa(qh[:, i:i + 1], case.k.reshape(T, nkv, hd)[:, kh][None, None].float(),
+                            case.v.reshape(T, nkv, hd)[:, kh][None, None].float(), True,
+                            case.scale)[0, 0]
+        assert_attention_close(fresh[:, h], want, f"head {h}")

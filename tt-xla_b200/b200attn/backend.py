@@ -1,0 +1,544 @@
+"""Attention backend classes with the surface of tt-xla's vLLM plugin backend
+(integrations/vllm_plugin/vllm_tt/attention_impls/attention.py), running on b200attn's CUDA
+kernels instead of `torch.ops.tt.*` custom calls lowered through PJRT.
+
+    TTAttentionBackend         (attention.py:89-160)  -> B200AttentionBackend
+    TTAttentionMetadataBuilder (attention.py:56-86)   -> B200AttentionMetadataBuilder
+    TTMetadata                 (attention.py:177-218) -> B200Metadata
+    TTAttentionBackendImpl     (attention.py:221-668) -> B200AttentionBackendImpl
+
+Two metadata forms reach `forward`:
+  * the plugin's own: `[users x padded tokens]` rows with `cache_position`, `page_table`,
+    `fill_page_table`, `batch_idx`, `chunk_start_idx`, `num_users` (what TTModelRunner
+    builds, model_runner.py:1894-2016);
+  * vLLM's flattened varlen form (`query_start_loc`, `seq_lens`, `block_table`,
+    `slot_mapping`), which B200AttentionMetadataBuilder.build derives from
+    CommonAttentionMetadata; decode rows go to the split-KV kernel and prefill / chunk rows
+    to the tcgen05 kernel in the same forward.
+"""
+from __future__ import annotations
+
+from collections import namedtuple
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from . import ops
+
+# head_size must be a multiple of 32 on the reference device; page accounting keeps that
+# padding rule (attention.py:37-38, 721-771).
+HEAD_SIZE_ALIGNMENT = 32
+
+STR_DTYPE_TO_TORCH_DTYPE = {
+    "half": torch.half,
+    "bfloat16": torch.bfloat16,
+    "float": torch.float,
+    "fp8": torch.float8_e4m3fn,
+    "fp8_e4m3": torch.float8_e4m3fn,
+    "fp8_e5m2": torch.float8_e5m2,
+    "int8": torch.int8,
+    "uint8": torch.uint8,
+}
+
+DECODER, ENCODER, ENCODER_ONLY = "decoder", "encoder", "encoder_only"
+
+
+def cdiv(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+@dataclass
+class B200Metadata:
+    """Per-step attention metadata; the first nine fields are TTMetadata's (attention.py:177-218),
+    the rest carry vLLM's varlen form."""
+
+    cache_position: Optional[torch.Tensor] = None   # [users] i32 = seq_len-1; -1 on padded rows
+    attn_mask: Optional[torch.Tensor] = None        # always None on the generative path
+    page_table: Optional[torch.Tensor] = None       # [users, nblk] i32, logical block order
+    is_causal: bool = True
+    fill_page_table: Optional[torch.Tensor] = None  # page_table rolled left by computed blocks
+    dp_size: int = 1
+    chunk_start_idx: Optional[torch.Tensor] = None  # [1] i32 shared prefix length, or None
+    batch_idx: Optional[torch.Tensor] = None        # [users] i32
+    num_users: Optional[int] = None
+    # ---- vLLM varlen form
+    slot_mapping: Optional[torch.Tensor] = None     # [tokens] i64
+    query_start_loc: Optional[torch.Tensor] = None  # [seqs+1] i32, device
+    query_start_loc_cpu: Optional[torch.Tensor] = None
+    seq_lens: Optional[torch.Tensor] = None         # [seqs] i32, device
+    block_table: Optional[torch.Tensor] = None      # [seqs, nblk] i32
+    num_decodes: int = 0                            # leading rows with one query token
+    max_seq_len: int = 0
+    # derived once per step by the builder (shared by all layers)
+    decode_cur_pos: Optional[torch.Tensor] = None
+    prefill_cu_q: Optional[torch.Tensor] = None
+    prefill_cu_q_cpu: Optional[torch.Tensor] = None
+    prefill_q_start: Optional[torch.Tensor] = None
+    extra: dict = field(default_factory=dict)
+
+    def __post_init__(self):
+        # attention.py:210-212: fill_page_table defaults to page_table.
+        if self.fill_page_table is None:
+            self.fill_page_table = self.page_table
+
+    @property
+    def is_varlen(self) -> bool:
+        return self.query_start_loc is not None
+
+
+class B200AttentionMetadataBuilder:
+    """Turns vLLM's CommonAttentionMetadata into B200Metadata.  The reference's builder is a stub
+    (attention.py:56-86) because its runner fills TTMetadata itself; on CUDA, vLLM's runner
+    calls `build` once per step and hands the result to every layer."""
+
+    reorder_batch_threshold = 1  # decode rows (one query token) are ordered first by vLLM
+
+    def __init__(self, kv_cache_spec=None, layer_names=None, vllm_config=None, device=None):
+        self.kv_cache_spec = kv_cache_spec
+        self.layer_names = layer_names
+        self.vllm_config = vllm_config
+        self.device = device
+
+    def build(self, common_prefix_len: int, common_attn_metadata, fast_build: bool = False):
+        m = common_attn_metadata
+        qsl = getattr(m, "query_start_loc", None)
+        if qsl is None:
+            # Same minimal object the reference builder returns.
+            return B200Metadata(is_causal=getattr(m, "causal", True))
+        qsl_cpu = getattr(m, "query_start_loc_cpu", None)
+        if qsl_cpu is None:
+            qsl_cpu = qsl.cpu()
+        return build_varlen_metadata(
+            query_start_loc=qsl,
+            query_start_loc_cpu=qsl_cpu,
+            seq_lens=m.seq_lens,
+            block_table=m.block_table_tensor,
+            slot_mapping=m.slot_mapping,
+            max_seq_len=int(getattr(m, "max_seq_len", 0) or 0),
+            is_causal=getattr(m, "causal", True),
+        )
+
+
+def build_varlen_metadata(
+    query_start_loc: torch.Tensor,
+    query_start_loc_cpu: torch.Tensor,
+    seq_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    max_seq_len: int = 0,
+    is_causal: bool = True,
+) -> B200Metadata:
+    """Derives the per-kernel index tensors from vLLM's varlen fields.  Rows whose query length
+    is 1 must come first (vLLM's decode-first batch order)."""
+    qsl_cpu = query_start_loc_cpu.to(torch.int32)
+    q_lens = qsl_cpu[1:] - qsl_cpu[:-1]
+    num_seqs = q_lens.numel()
+    num_decodes = 0
+    while num_decodes < num_seqs and int(q_lens[num_decodes]) == 1:
+        num_decodes += 1
+    # A one-token row after a longer one is served as a prefill row of length 1.
+    seq_lens = seq_lens.to(torch.int32)
+    qsl = query_start_loc.to(torch.int32)
+    md = B200Metadata(
+        is_causal=is_causal,
+        slot_mapping=slot_mapping,
+        query_start_loc=qsl,
+        query_start_loc_cpu=qsl_cpu,
+        seq_lens=seq_lens,
+        block_table=block_table,
+        num_decodes=num_decodes,
+        max_seq_len=max_seq_len,
+        num_users=num_seqs,
+    )
+    if num_decodes > 0:
+        md.decode_cur_pos = (seq_lens[:num_decodes] - 1).contiguous()
+    if num_decodes < num_seqs:
+        base = int(qsl_cpu[num_decodes])
+        md.prefill_cu_q_cpu = (qsl_cpu[num_decodes:] - base).contiguous()
+        md.prefill_cu_q = (qsl[num_decodes:] - base).contiguous()
+        # first query row of sequence s sits at position seq_len - q_len
+        md.prefill_q_start = (
+            seq_lens[num_decodes:] - (qsl[num_decodes + 1:] - qsl[num_decodes:-1])
+        ).contiguous()
+    return md
+
+
+class B200AttentionBackend:
+    """Static descriptors of the backend (attention.py:89-160)."""
+
+    accept_output_buffer = True
+    forward_includes_kv_cache_update = True
+    supported_dtypes = [torch.bfloat16]
+    supported_kv_cache_dtypes = ["auto", "bfloat16"]
+    supported_head_sizes = [64, 128]
+    supported_block_sizes = [32, 64]
+
+    @staticmethod
+    def get_name() -> str:
+        return "CUSTOM"
+
+    @staticmethod
+    def get_impl_cls():
+        return B200AttentionBackendImpl
+
+    @staticmethod
+    def get_builder_cls():
+        return B200AttentionMetadataBuilder
+
+    @staticmethod
+    def get_metadata_cls():
+        return B200Metadata
+
+    @staticmethod
+    def get_kv_cache_shape(
+        num_blocks: int,
+        block_size: int,
+        num_kv_heads: int,
+        head_size: int,
+        cache_dtype_str: str = "auto",
+    ) -> tuple[int, ...]:
+        # One of the two separate K / V tensors per layer (attention.py:103-112).
+        return (num_blocks, num_kv_heads, block_size, head_size)
+
+    @staticmethod
+    def get_fused_kv_cache_shape(
+        num_blocks: int, block_size: int, num_kv_heads: int, head_size: int
+    ) -> tuple[int, ...]:
+        # vLLM's CUDA runner allocates one tensor per layer; index 0 / 1 of this shape are the
+        # K and V tensors above, bit-identical in layout.
+        return (2, num_blocks, num_kv_heads, block_size, head_size)
+
+    @staticmethod
+    def swap_blocks(src_kv_cache, dst_kv_cache, src_to_dst) -> None:
+        raise RuntimeError("swap_blocks is not used for the B200 backend.")
+
+    @staticmethod
+    def get_min_page_size(max_model_len: int, max_num_seqs: int) -> int:
+        # attention.py:126-135 (page-table bytes kept under half a MiB), as plain arithmetic.
+        max_num_page_per_req = 1024 * 1024 // 2 // max_num_seqs // 4
+        min_page_size = cdiv(max_model_len, max_num_page_per_req)
+        return 1 << (min_page_size - 1).bit_length()
+
+    @staticmethod
+    def get_max_num_seqs(model_len: int, page_size: int) -> int:
+        # attention.py:137-140.
+        num_page_per_req = cdiv(model_len, page_size)
+        return 1024 * 1024 // 2 // num_page_per_req // 4
+
+    @staticmethod
+    def get_page_size(vllm_config=None) -> int:
+        # attention.py:146-152: the reference pins 32.
+        return 32
+
+    @classmethod
+    def supports_head_size(cls, head_size: int) -> bool:
+        return head_size in cls.supported_head_sizes
+
+    @classmethod
+    def supports_block_size(cls, block_size: int) -> bool:
+        return block_size in cls.supported_block_sizes
+
+
+def dtype_bits(dtype: torch.dtype) -> int:
+    """attention.py:721-737."""
+    if dtype.is_floating_point:
+        return torch.finfo(dtype).bits
+    if dtype == torch.bool:
+        return 8
+    return torch.iinfo(dtype).bits
+
+
+def get_dtype_packing(dtype: torch.dtype) -> int:
+    """attention.py:740-747: elements per 32-bit word."""
+    bits = dtype_bits(dtype)
+    if 32 % bits != 0:
+        raise ValueError(f"The bit width must be divisible by 32, but got bits={bits}")
+    return 32 // bits
+
+
+def get_page_size_bytes(
+    block_size: int, num_kv_heads: int, head_size: int, kv_cache_dtype: torch.dtype
+) -> int:
+    """attention.py:750-771: bytes of one page holding K and V, head_size padded to 32."""
+    padded_head_size = cdiv(head_size, HEAD_SIZE_ALIGNMENT) * HEAD_SIZE_ALIGNMENT
+    num_combined_kv_heads = num_kv_heads * 2
+    packing = get_dtype_packing(kv_cache_dtype)
+    num_combined_kv_heads = cdiv(num_combined_kv_heads, packing) * packing
+    kv_cache_dtype_bits = dtype_bits(kv_cache_dtype)
+    return block_size * num_combined_kv_heads * padded_head_size * kv_cache_dtype_bits // 8
+
+
+AttentionInputs = namedtuple(
+    "AttentionInputs",
+    [
+        "query", "key", "value", "orig_query_shape", "orig_query_ndim", "users",
+        "query_num_tokens", "is_prefill", "users_kv", "kv_num_tokens",
+    ],
+)
+
+
+class B200AttentionBackendImpl:
+    """Per-layer attention implementation (attention.py:221-668)."""
+
+    def __init__(
+        self,
+        num_heads: int,
+        head_size: int,
+        scale: float,
+        num_kv_heads: int,
+        alibi_slopes: Optional[list] = None,
+        sliding_window: Optional[int] = None,
+        kv_cache_dtype: str = "auto",
+        logits_soft_cap: Optional[float] = None,
+        attn_type: str = DECODER,
+        kv_sharing_target_layer_name: Optional[str] = None,
+        sinks: Optional[torch.Tensor] = None,
+    ) -> None:
+        self.num_heads = num_heads
+        self.head_size = head_size
+        self.scale = float(scale)
+        self.num_kv_heads = num_kv_heads
+        self.sliding_window = sliding_window
+        self.logits_soft_cap = logits_soft_cap
+        self.kv_sharing_target_layer_name = kv_sharing_target_layer_name
+        self.num_queries_per_kv = self.num_heads // self.num_kv_heads
+        if alibi_slopes is not None:
+            raise NotImplementedError("Alibi slopes is not supported.")
+        if str(getattr(attn_type, "value", attn_type)) not in (DECODER, ENCODER, ENCODER_ONLY):
+            raise NotImplementedError(
+                f"B200 attention only supports encoder or decoder attention, but got {attn_type}."
+            )
+        self.attn_type = attn_type
+        self.kv_cache_quantized_dtype = None
+        if kv_cache_dtype not in ("auto", "bfloat16"):
+            # The reference maps fp8/int8 names to torch dtypes (attention.py:259-263); the CUDA
+            # kernels store bf16 only and refuse the rest instead of silently converting.
+            raise NotImplementedError(
+                f"kv_cache_dtype {kv_cache_dtype!r} is not supported (bf16 cache only)"
+            )
+        if sliding_window is not None:
+            raise NotImplementedError("sliding_window attention is not supported")
+        if logits_soft_cap is not None:
+            raise NotImplementedError("logits_soft_cap is not supported")
+        self.sinks = sinks
+        if self.sinks is not None:
+            raise NotImplementedError("attention sinks are not supported")
+
+    # ------------------------------------------------------------------ forward
+    def forward(
+        self,
+        layer,
+        query: torch.Tensor,
+        key: torch.Tensor,
+        value: torch.Tensor,
+        kv_cache,
+        attn_metadata: B200Metadata,
+        output: Optional[torch.Tensor] = None,
+        output_scale: Optional[torch.Tensor] = None,
+        output_block_scale: Optional[torch.Tensor] = None,
+    ) -> Optional[torch.Tensor]:
+        """query [tokens, nq*hd], key/value [tokens, nkv*hd], kv_cache = [k_cache, v_cache]
+        (or one tensor [2, nb, nkv, bs, hd]); writes `output` in place (attention.py:273-336)."""
+        assert attn_metadata is not None, "B200 attention requires metadata."
+        assert output is not None, "B200 attention requires an output buffer."
+        if output_scale is not None or output_block_scale is not None:
+            raise NotImplementedError("fused output quantisation is not supported")
+        kv_pair = self._split_kv_cache(kv_cache)
+        if attn_metadata.is_varlen:
+            self._forward_varlen(query, key, value, kv_pair, attn_metadata, output)
+            return output
+
+        inputs = self._prepare_inputs(query, key, value, attn_metadata)
+        has_cache = kv_pair is not None
+        if has_cache and self.kv_sharing_target_layer_name is None:
+            self._handle_paged_attention(inputs, kv_pair, attn_metadata)
+        if inputs.is_prefill:
+            self._compute_full_attention(inputs, kv_pair, attn_metadata, output)
+        else:
+            if not has_cache:
+                raise ValueError("decode attention needs the paged KV cache")
+            self._compute_decode_attention(inputs, kv_pair, attn_metadata, output)
+        return output
+
+    @staticmethod
+    def _split_kv_cache(kv_cache):
+        """[k_cache, v_cache] (the reference's form, model_runner.py:4603-4609), or vLLM's single
+        [2, nb, nkv, bs, hd] tensor; None while profiling with a placeholder."""
+        if isinstance(kv_cache, (list, tuple)):
+            if len(kv_cache) >= 2 and kv_cache[0].numel() > 0:
+                return kv_cache[0], kv_cache[1]
+            return None
+        if isinstance(kv_cache, torch.Tensor) and kv_cache.dim() == 5 and kv_cache.shape[0] == 2:
+            return kv_cache[0], kv_cache[1]
+        return None
+
+    def _normalize_to_attention_format(
+        self, tensor: torch.Tensor, tensor_name: str, expected_num_heads: int,
+        expected_head_size: int, num_users: int,
+    ) -> torch.Tensor:
+        """[users, tokens, heads, head_size] view; same acceptance rules and messages as
+        attention.py:338-379."""
+        if tensor.ndim < 2:
+            raise ValueError(
+                f"{tensor_name} must have rank >= 2, got shape={tuple(tensor.shape)}"
+            )
+        expected_hidden = expected_num_heads * expected_head_size
+        if tensor.ndim == 2 and tensor.shape[-1] == expected_hidden:
+            normalized = tensor.reshape(-1, expected_num_heads, expected_head_size)
+        elif (
+            tensor.ndim == 3
+            and tensor.shape[-2] == expected_num_heads
+            and tensor.shape[-1] == expected_head_size
+        ):
+            normalized = tensor
+        else:
+            raise ValueError(
+                f"{tensor_name} must be either a flattened-token tensor with "
+                f"shape[-1] == {expected_hidden} or a head-shaped tensor with "
+                f"shape[-2:] == ({expected_num_heads}, {expected_head_size}); "
+                f"got shape={tuple(tensor.shape)}"
+            )
+        total_tokens = normalized.shape[0]
+        if total_tokens % num_users != 0:
+            raise ValueError(
+                f"{tensor_name} total tokens ({total_tokens}) must be divisible "
+                f"by num_users ({num_users})"
+            )
+        return normalized.reshape(num_users, -1, expected_num_heads, expected_head_size)
+
+    def _prepare_inputs(self, query, key, value, attn_metadata: B200Metadata) -> AttentionInputs:
+        """attention.py:381-459."""
+        num_users = attn_metadata.num_users
+        assert num_users is not None, "num_users must be provided in attn_metadata."
+        orig_query_shape, orig_query_ndim = query.shape, query.ndim
+        query = self._normalize_to_attention_format(
+            query, "query", self.num_heads, self.head_size, num_users
+        )
+        key = self._normalize_to_attention_format(
+            key, "key", self.num_kv_heads, self.head_size, num_users
+        )
+        value = self._normalize_to_attention_format(
+            value, "value", self.num_kv_heads, self.head_size, num_users
+        )
+        if key.shape != value.shape:
+            raise ValueError(
+                f"key and value must match after normalization, got "
+                f"key={tuple(key.shape)} value={tuple(value.shape)}"
+            )
+        query_num_tokens = query.shape[1]
+        return AttentionInputs(
+            query=query, key=key, value=value, orig_query_shape=orig_query_shape,
+            orig_query_ndim=orig_query_ndim, users=num_users,
+            query_num_tokens=query_num_tokens, is_prefill=query_num_tokens > 1,
+            users_kv=key.shape[0], kv_num_tokens=key.shape[1],
+        )
+
+    def _handle_paged_attention(self, inputs, kv_pair, attn_metadata: B200Metadata) -> None:
+        """KV-cache write (attention.py:461-515): one launch covers K and V."""
+        k_cache, v_cache = kv_pair
+        if not inputs.is_prefill:
+            ops.paged_update_cache(
+                k_cache, v_cache, inputs.key[:, 0], inputs.value[:, 0],
+                attn_metadata.cache_position, attn_metadata.page_table,
+            )
+            return
+        batch_idxs = attn_metadata.batch_idx
+        assert batch_idxs is not None, "batch_idx must be provided for prefill."
+        if attn_metadata.dp_size > 1:
+            local_batch = inputs.key.shape[0] // attn_metadata.dp_size
+            batch_idxs = batch_idxs % local_batch
+        ops.paged_fill_cache(
+            k_cache, v_cache, inputs.key, inputs.value, attn_metadata.fill_page_table, batch_idxs
+        )
+
+    def _uniform_cu_q(self, users: int, tokens: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+        key = (users, tokens, str(device))
+        cache = self.__dict__.setdefault("_cu_q_cache", {})
+        if key not in cache:
+            host = torch.arange(users + 1, dtype=torch.int32) * tokens
+            cache[key] = (host, host.to(device))
+        return cache[key]
+
+    def _compute_full_attention(self, inputs, kv_pair, attn_metadata: B200Metadata, output) -> None:
+        """Prefill (attention.py:517-598): chunk over the paged prefix when chunk_start_idx is
+        set, dense causal attention on the fresh K/V otherwise."""
+        if attn_metadata.attn_mask is not None or not attn_metadata.is_causal:
+            raise NotImplementedError(
+                "only causal attention without an explicit mask is supported (the generative "
+                "path; model_runner.py:2004-2016)"
+            )
+        users, tokens = inputs.users, inputs.query_num_tokens
+        q = inputs.query.reshape(users * tokens, self.num_heads, self.head_size)
+        out = output.reshape(users * tokens, self.num_heads, self.head_size)
+        cu_host, cu_dev = self._uniform_cu_q(users, tokens, q.device)
+        has_cache = kv_pair is not None
+        shared_kv_mode = self.kv_sharing_target_layer_name is not None and has_cache
+        if attn_metadata.chunk_start_idx is not None and has_cache and not shared_kv_mode:
+            q_start = attn_metadata.chunk_start_idx.reshape(-1)[:1].to(torch.int32).expand(users)
+            ops.prefill(
+                q, kv_pair[0], kv_pair[1], cu_host, scale=self.scale,
+                page_table=attn_metadata.page_table, q_start=q_start.contiguous(), out=out,
+                cu_q=cu_dev,
+            )
+        elif shared_kv_mode:
+            # Shared-KV layers read the target layer's cache (attention.py:562-574); the kernel
+            # reads pages directly, so no dense gather is needed.
+            ops.prefill(
+                q, kv_pair[0], kv_pair[1], cu_host, scale=self.scale,
+                page_table=attn_metadata.page_table, q_start=None, out=out, cu_q=cu_dev,
+            )
+        else:
+            k = inputs.key.reshape(users * tokens, self.num_kv_heads, self.head_size)
+            v = inputs.value.reshape(users * tokens, self.num_kv_heads, self.head_size)
+            ops.prefill(q, k, v, cu_host, scale=self.scale, out=out, cu_q=cu_dev)
+
+    def _compute_decode_attention(self, inputs, kv_pair, attn_metadata: B200Metadata, output) -> None:
+        """attention.py:634-668."""
+        if attn_metadata.attn_mask is not None or not attn_metadata.is_causal:
+            raise NotImplementedError("decode supports the causal cur_pos form only")
+        users = inputs.users
+        ops.paged_decode(
+            inputs.query.reshape(users, self.num_heads, self.head_size),
+            kv_pair[0], kv_pair[1], attn_metadata.page_table, attn_metadata.cache_position,
+            scale=self.scale,
+            out=output.reshape(users, self.num_heads, self.head_size),
+            max_context_len=attn_metadata.max_seq_len,
+        )
+
+    # ------------------------------------------------------------------ vLLM varlen form
+    def _forward_varlen(self, query, key, value, kv_pair, md: B200Metadata, output) -> None:
+        if kv_pair is None:
+            # Memory-profiling run before the cache exists: nothing to attend to.
+            output.zero_()
+            return
+        nq, nkv, hd = self.num_heads, self.num_kv_heads, self.head_size
+        n_tok = int(md.query_start_loc_cpu[-1])
+        q = query[:n_tok].reshape(n_tok, nq, hd)
+        out = output[:n_tok].reshape(n_tok, nq, hd)
+        if self.kv_sharing_target_layer_name is None:
+            ops.kv_scatter_slots(
+                kv_pair[0], kv_pair[1], key[:n_tok].reshape(n_tok, nkv, hd),
+                value[:n_tok].reshape(n_tok, nkv, hd), md.slot_mapping[:n_tok],
+            )
+        nd = md.num_decodes
+        if nd > 0:
+            ops.paged_decode(
+                q[:nd], kv_pair[0], kv_pair[1], md.block_table[:nd], md.decode_cur_pos,
+                scale=self.scale, out=out[:nd], max_context_len=md.max_seq_len,
+            )
+        if md.prefill_cu_q_cpu is not None:
+            ops.prefill(
+                q[nd:], kv_pair[0], kv_pair[1], md.prefill_cu_q_cpu, scale=self.scale,
+                page_table=md.block_table[nd:], q_start=md.prefill_q_start, out=out[nd:],
+                cu_q=md.prefill_cu_q,
+            )
+
+
+def write_to_kv_cache(key, value, kv_cache, slot_mapping, *unused, **unused_kw) -> None:
+    """Slot-mapping cache write (attention.py:671-716) on the live [k_cache, v_cache] layout."""
+    k_cache, v_cache = kv_cache[0], kv_cache[1]
+    nkv, hd = k_cache.shape[1], k_cache.shape[3]
+    ops.kv_scatter_slots(
+        k_cache, v_cache, key.reshape(-1, nkv, hd), value.reshape(-1, nkv, hd), slot_mapping
+    )

@@ -1,0 +1,357 @@
+"""CUDA ops of the attention / KV-cache path, one per `torch.ops.tt.*` op the reference plugin
+calls (python_package/tt_torch/custom_ops.py).  Each takes torch CUDA tensors, validates the
+layout the reference documents, and calls the C ABI on torch's current stream.
+
+The reference ops are functional (they return a new cache, which the caller copies back,
+attention.py:513-515); these update the caches in place, which is what that copy-back amounts
+to.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "b200attn ops run on CUDA tensors only (there is no CPU path); got a "
+                f"{t.device.type} tensor"
+            )
+
+
+def _check_cache(k_cache: torch.Tensor, v_cache: torch.Tensor) -> tuple[int, int, int, int]:
+    if k_cache.dim() != 4 or k_cache.shape != v_cache.shape:
+        raise ValueError(
+            "k_cache and v_cache must both be [num_blocks, num_kv_heads, block_size, head_size]; "
+            f"got {tuple(k_cache.shape)} and {tuple(v_cache.shape)}"
+        )
+    if k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise ValueError("only bfloat16 caches are supported")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("caches must be contiguous")
+    nb, nkv, bs, hd = k_cache.shape
+    return nb, nkv, bs, hd
+
+
+def _token_major(x: torch.Tensor, nheads: int, hd: int, name: str) -> tuple[torch.Tensor, int]:
+    """Returns a [tokens, nheads, hd] view whose last two dims are dense, and its row stride."""
+    x = x.reshape(-1, nheads, hd) if x.dim() != 3 else x
+    if x.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be bfloat16")
+    if x.stride(2) != 1 or x.stride(1) != hd:
+        x = x.contiguous()
+    return x, x.stride(0) if x.shape[0] > 1 else max(x.stride(0), nheads * hd)
+
+
+def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.int32:
+        raise ValueError(f"{name} must be int32, got {t.dtype}")
+    return t
+
+
+def paged_update_cache(
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    update_indices: torch.Tensor,
+    page_table: torch.Tensor,
+) -> None:
+    """Decode-step KV write: `tt.paged_update_cache` for K and V in one launch
+    (custom_ops.py:962-1013).  `key`/`value`: [users, nkv, hd] (the reference's
+    [1, users, nkv, hd] is accepted too)."""
+    _need_cuda(k_cache, v_cache, key, value, update_indices, page_table)
+    nb, nkv, bs, hd = _check_cache(k_cache, v_cache)
+    key, kstride = _token_major(key, nkv, hd, "key")
+    value, vstride = _token_major(value, nkv, hd, "value")
+    if key.shape != value.shape:
+        raise ValueError("key and value must have the same shape")
+    if kstride != vstride:
+        value = value.contiguous()
+        key = key.contiguous()
+        kstride = nkv * hd
+    users = update_indices.shape[0]
+    if key.shape[0] != users or page_table.shape[0] < users:
+        raise ValueError("key/value rows, update_indices and page_table rows must agree")
+    _i32(update_indices, "update_indices")
+    _i32(page_table, "page_table")
+    if page_table.stride(1) != 1 or not update_indices.is_contiguous():
+        raise ValueError("page_table rows and update_indices must be dense")
+    L = _lib.lib()
+    _lib.check(
+        "b200attn_paged_update_cache",
+        L.b200attn_paged_update_cache(
+            k_cache.data_ptr(), v_cache.data_ptr(), key.data_ptr(), value.data_ptr(), kstride,
+            update_indices.data_ptr(), page_table.data_ptr(), page_table.stride(0),
+            page_table.shape[1], users, nkv, hd, bs, nb, _stream(k_cache),
+        ),
+    )
+
+
+def paged_fill_cache(
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    fill_page_table: torch.Tensor,
+    batch_idx: Optional[torch.Tensor] = None,
+) -> None:
+    """Prefill / chunk KV write: `tt.paged_fill_cache` for K and V, all users in one launch
+    (custom_ops.py:1016-1104).  `key`/`value`: [users, tokens, nkv, hd] token-major (the layout
+    the plugin holds before it transposes for the reference op, attention.py:487-488)."""
+    _need_cuda(k_cache, v_cache, key, value, fill_page_table, batch_idx)
+    nb, nkv, bs, hd = _check_cache(k_cache, v_cache)
+    if key.dim() != 4 or key.shape != value.shape or key.shape[2] != nkv or key.shape[3] != hd:
+        raise ValueError(
+            f"key/value must be [users, tokens, {nkv}, {hd}], got {tuple(key.shape)}"
+        )
+    users, tokens = key.shape[0], key.shape[1]
+    if not key.is_contiguous():
+        key = key.contiguous()
+    if not value.is_contiguous():
+        value = value.contiguous()
+    _i32(fill_page_table, "fill_page_table")
+    if fill_page_table.stride(1) != 1:
+        raise ValueError("fill_page_table rows must be dense")
+    if batch_idx is not None:
+        _i32(batch_idx, "batch_idx")
+        if batch_idx.numel() != users or not batch_idx.is_contiguous():
+            raise ValueError("batch_idx must hold one dense entry per user")
+    L = _lib.lib()
+    _lib.check(
+        "b200attn_paged_fill_cache",
+        L.b200attn_paged_fill_cache(
+            k_cache.data_ptr(), v_cache.data_ptr(), key.data_ptr(), value.data_ptr(), nkv * hd,
+            fill_page_table.data_ptr(), fill_page_table.stride(0), fill_page_table.shape[1],
+            batch_idx.data_ptr() if batch_idx is not None else None,
+            users, tokens, nkv, hd, bs, nb, _stream(k_cache),
+        ),
+    )
+
+
+def kv_scatter_slots(
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> None:
+    """KV write addressed by vLLM's `slot_mapping` (int64, negative = skip); the live-layout
+    counterpart of `write_to_kv_cache` (attention.py:671-716)."""
+    _need_cuda(k_cache, v_cache, key, value, slot_mapping)
+    nb, nkv, bs, hd = _check_cache(k_cache, v_cache)
+    key, kstride = _token_major(key, nkv, hd, "key")
+    value, vstride = _token_major(value, nkv, hd, "value")
+    if kstride != vstride:
+        key, value = key.contiguous(), value.contiguous()
+        kstride = nkv * hd
+    if slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a dense int64 tensor")
+    n = slot_mapping.numel()
+    if key.shape[0] < n or value.shape[0] < n:
+        raise ValueError("fewer key/value rows than slots")
+    L = _lib.lib()
+    _lib.check(
+        "b200attn_kv_scatter_slots",
+        L.b200attn_kv_scatter_slots(
+            k_cache.data_ptr(), v_cache.data_ptr(), key.data_ptr(), value.data_ptr(), kstride,
+            slot_mapping.data_ptr(), n, nkv, hd, bs, nb, _stream(k_cache),
+        ),
+    )
+
+
+def decode_auto_splits(users: int, nkv: int, bs: int, max_context_len: int) -> int:
+    return _lib.lib().b200attn_decode_auto_splits(users, nkv, bs, max_context_len)
+
+
+def decode_workspace_bytes(users: int, nq: int, hd: int, splits: int) -> int:
+    return _lib.lib().b200attn_decode_workspace_bytes(users, nq, hd, splits)
+
+
+def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    """Split-KV scratch, cached per (device, stream) and grown on demand.  torch owns the
+    memory; the C library never allocates."""
+    if nbytes == 0:
+        return None
+    key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def paged_decode(
+    query: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    page_table: torch.Tensor,
+    cur_pos: torch.Tensor,
+    scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    num_splits: int = 0,
+    max_context_len: int = 0,
+    workspace: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Paged GQA decode attention: `tt.paged_scaled_dot_product_attention_decode` with
+    is_causal=True and cur_pos_tensor (custom_ops.py:1198-1331).  `query`: [users, nq, hd]
+    (or the reference's [1, users, nq, hd]); returns / fills `out` of the same shape."""
+    _need_cuda(query, k_cache, v_cache, page_table, cur_pos, out)
+    nb, nkv, bs, hd = _check_cache(k_cache, v_cache)
+    orig_shape = query.shape
+    if query.dim() == 4:
+        if query.shape[0] != 1:
+            raise ValueError("4-D query must be [1, users, nq, hd]")
+        query = query[0]
+    if query.dim() != 3 or query.shape[2] != hd:
+        raise ValueError(f"query must be [users, nq, {hd}], got {tuple(orig_shape)}")
+    users, nq = query.shape[0], query.shape[1]
+    if nq % nkv != 0:
+        raise ValueError(f"num_q_heads {nq} is not a multiple of num_kv_heads {nkv}")
+    q, qstride = _token_major(query, nq, hd, "query")
+    if out is None:
+        out_t = torch.empty((users, nq, hd), dtype=torch.bfloat16, device=query.device)
+    else:
+        out_t = out.reshape(users, nq, hd) if out.dim() != 3 else out
+        if out_t.dtype != torch.bfloat16 or out_t.stride(2) != 1 or out_t.stride(1) != hd:
+            raise ValueError("out must be a dense-row bfloat16 tensor")
+        if out_t.data_ptr() != out.data_ptr():
+            raise ValueError("out must be viewable as [users, nq, hd] without a copy")
+    ostride = out_t.stride(0) if users > 1 else max(out_t.stride(0), nq * hd)
+    _i32(page_table, "page_table")
+    _i32(cur_pos, "cur_pos")
+    if page_table.stride(1) != 1 or not cur_pos.is_contiguous() or cur_pos.numel() != users:
+        raise ValueError("page_table rows must be dense and cur_pos must hold one entry per user")
+    if scale is None:
+        scale = hd ** -0.5
+    L = _lib.lib()
+    if num_splits == 0:
+        ctx = max_context_len if max_context_len > 0 else page_table.shape[1] * bs
+        num_splits = L.b200attn_decode_auto_splits(users, nkv, bs, ctx)
+    need = L.b200attn_decode_workspace_bytes(users, nq, hd, num_splits)
+    ws = workspace if workspace is not None else _workspace(query.device, need)
+    _lib.check(
+        "b200attn_paged_decode",
+        L.b200attn_paged_decode(
+            out_t.data_ptr(), ostride, q.data_ptr(), qstride, k_cache.data_ptr(),
+            v_cache.data_ptr(), page_table.data_ptr(), page_table.stride(0), page_table.shape[1],
+            cur_pos.data_ptr(), users, nq, nkv, hd, bs, nb, float(scale), max_context_len,
+            num_splits, ws.data_ptr() if ws is not None else None,
+            ws.numel() * ws.element_size() if ws is not None else 0, _stream(query),
+        ),
+    )
+    if out is not None:
+        return out
+    return out_t.reshape(orig_shape)
+
+
+def prefill(
+    query: torch.Tensor,
+    k_src: torch.Tensor,
+    v_src: torch.Tensor,
+    cu_q_host: torch.Tensor,
+    scale: Optional[float] = None,
+    page_table: Optional[torch.Tensor] = None,
+    q_start: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    cu_q: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Causal varlen prefill (`tt.scaled_dot_product_attention`, custom_ops.py:635-742) when
+    `page_table` is None and `k_src`/`v_src` are the fresh [tokens, nkv, hd] K/V of the same
+    tokens; chunked prefill over the paged cache
+    (`tt.chunked_scaled_dot_product_attention`, custom_ops.py:1334-1443) when `page_table` is
+    given and `k_src`/`v_src` are the caches.  `query`: [tokens, nq, hd] with sequence s owning
+    rows cu_q[s]:cu_q[s+1]; `q_start[s]` is the absolute position of its first row."""
+    _need_cuda(query, k_src, v_src, page_table, q_start, out, cu_q)
+    if cu_q_host.is_cuda or cu_q_host.dtype != torch.int32 or not cu_q_host.is_contiguous():
+        raise ValueError("cu_q_host must be a dense int32 CPU tensor")
+    num_seqs = cu_q_host.numel() - 1
+    if query.dim() != 3:
+        raise ValueError(f"query must be [tokens, nq, hd], got {tuple(query.shape)}")
+    total_q, nq, hd = query.shape
+    q, qstride = _token_major(query, nq, hd, "query")
+    paged = page_table is not None
+    if paged:
+        nb, nkv, bs, _hd = _check_cache(k_src, v_src)
+        if _hd != hd:
+            raise ValueError("cache head_size differs from query head_size")
+        _i32(page_table, "page_table")
+        if page_table.stride(1) != 1 or page_table.shape[0] < num_seqs:
+            raise ValueError("page_table must have one dense row per sequence")
+        kstride = 0
+        k, v = k_src, v_src
+    else:
+        if q_start is not None:
+            raise ValueError("q_start needs the paged form (the prefix lives in the cache)")
+        if k_src.dim() != 3 or k_src.shape != v_src.shape or k_src.shape[2] != hd:
+            raise ValueError("fresh k_src/v_src must be [tokens, nkv, hd]")
+        if k_src.shape[0] != total_q:
+            raise ValueError("fresh K/V must cover the same tokens as the query")
+        nkv = k_src.shape[1]
+        k, kstride = _token_major(k_src, nkv, hd, "k_src")
+        v, vstride = _token_major(v_src, nkv, hd, "v_src")
+        if kstride != vstride:
+            k, v = k.contiguous(), v.contiguous()
+            kstride = nkv * hd
+        nb, bs = 0, 64
+    if nq % nkv != 0:
+        raise ValueError(f"num_q_heads {nq} is not a multiple of num_kv_heads {nkv}")
+    if q_start is not None:
+        _i32(q_start, "q_start")
+        if q_start.numel() != num_seqs or not q_start.is_contiguous():
+            raise ValueError("q_start must hold one dense entry per sequence")
+    if cu_q is None:
+        cu_q = cu_q_host.to(query.device, non_blocking=True)
+    _i32(cu_q, "cu_q")
+    if out is None:
+        out_t = torch.empty((total_q, nq, hd), dtype=torch.bfloat16, device=query.device)
+    else:
+        out_t = out.reshape(total_q, nq, hd) if out.dim() != 3 else out
+        if out_t.dtype != torch.bfloat16 or out_t.stride(2) != 1 or out_t.stride(1) != hd:
+            raise ValueError("out must be a dense-row bfloat16 tensor")
+        if out_t.data_ptr() != out.data_ptr():
+            raise ValueError("out must be viewable as [tokens, nq, hd] without a copy")
+    ostride = out_t.stride(0) if total_q > 1 else max(out_t.stride(0), nq * hd)
+    if scale is None:
+        scale = hd ** -0.5
+    L = _lib.lib()
+    _lib.check(
+        "b200attn_prefill",
+        L.b200attn_prefill(
+            out_t.data_ptr(), ostride, q.data_ptr(), qstride, k.data_ptr(), v.data_ptr(),
+            1 if paged else 0, kstride,
+            page_table.data_ptr() if paged else None,
+            page_table.stride(0) if paged else 0, page_table.shape[1] if paged else 0,
+            cu_q.data_ptr(), cu_q_host.data_ptr(),
+            q_start.data_ptr() if q_start is not None else None,
+            num_seqs, total_q, nq, nkv, hd, bs, nb, float(scale), _stream(query),
+        ),
+    )
+    return out if out is not None else out_t
+
+
+def read_error_word(device: Optional[torch.device] = None) -> int:
+    """Returns and clears the device diagnostics word (0 = clean, 1 = a bounded wait ran out,
+    2 = a page id or slot pointed outside the cache)."""
+    word = ctypes.c_int32(0)
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(dev):
+        _lib.check(
+            "b200attn_read_error_word",
+            _lib.lib().b200attn_read_error_word(
+                ctypes.byref(word), torch.cuda.current_stream(dev).cuda_stream
+            ),
+        )
+    return int(word.value)

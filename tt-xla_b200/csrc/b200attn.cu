@@ -1,0 +1,457 @@
+// Host side of the C ABI declared in include/b200attn.h: argument checks, tensor-map
+// encoding and kernel launches.  Single translation unit; built for sm_100a only.
+#include "../../include/b200attn.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "decode.cuh"
+#include "kv_scatter.cuh"
+#include "prefill.cuh"
+
+namespace b200attn {
+
+__device__ int g_err_word = 0;
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  int* err_word = nullptr;
+};
+
+static std::mutex g_mutex;
+static DeviceInfo g_devices[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+// Per-device set-up on first use: SM count, address of the diagnostics word, and the
+// driver's tensor-map encoder (looked up at run time so the library has no link-time
+// dependency on libcuda and still loads on a machine without a driver).
+static int get_device(DeviceInfo** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return B200ATTN_ERR_NO_DEVICE;
+  }
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceInfo& d = g_devices[dev];
+  if (!d.ready) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return B200ATTN_ERR_NO_DEVICE;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_err_word) != cudaSuccess) {
+      cudaGetLastError();
+      return B200ATTN_ERR_NO_DEVICE;
+    }
+    d.err_word = static_cast<int*>(p);
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) !=
+              cudaSuccess ||
+          q != cudaDriverEntryPointSuccess || !fn) {
+        cudaGetLastError();
+        return B200ATTN_ERR_NO_DEVICE;
+      }
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    d.ready = true;
+  }
+  *out = &d;
+  return B200ATTN_OK;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// bf16 matrix [rows, cols] with `row_stride` elements between rows; boxes of
+// [box_rows x 64 columns] land in shared memory with the 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                    uint64_t row_stride, uint32_t box_rows) {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ERR_TENSOR_MAP;
+}
+
+static int check_cache_geometry(int num_kv_heads, int head_size, int block_size,
+                                int64_t num_blocks) {
+  if (num_kv_heads <= 0 || num_blocks <= 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (head_size != 64 && head_size != 128) return B200ATTN_ERR_UNSUPPORTED;
+  if (block_size != 32 && block_size != 64) return B200ATTN_ERR_UNSUPPORTED;
+  if (num_blocks * num_kv_heads * block_size > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
+  return B200ATTN_OK;
+}
+
+// ------------------------------------------------------------------------------ scatter
+static int launch_scatter(int mode, ScatterParams& p, int head_size, void* stream) {
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (!p.k_cache || !p.v_cache || !p.k_new || !p.v_new) return B200ATTN_ERR_NULL_POINTER;
+  if (!aligned16(p.k_cache) || !aligned16(p.v_cache) || !aligned16(p.k_new) ||
+      !aligned16(p.v_new))
+    return B200ATTN_ERR_MISALIGNED;
+  p.vec_per_head = head_size / 8;
+  p.err_word = dev->err_word;
+  if (p.num_tokens == 0) return B200ATTN_OK;
+  const int64_t total = p.num_tokens * p.num_kv_heads * p.vec_per_head;
+  const int threads = 256;
+  int64_t blocks = (total + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(dev->sm_count) * 8;  // grid-stride beyond this
+  if (blocks > cap) blocks = cap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (mode) {
+    case kScatterSlots:
+      kv_scatter_kernel<kScatterSlots><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+      break;
+    case kScatterUpdate:
+      kv_scatter_kernel<kScatterUpdate><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+      break;
+    default:
+      kv_scatter_kernel<kScatterFill><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+      break;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+static int fill_scatter_common(ScatterParams& p, void* k_cache, void* v_cache, const void* k_new,
+                               const void* v_new, int64_t new_token_stride, int num_kv_heads,
+                               int head_size, int block_size, int64_t num_blocks) {
+  if (int rc = check_cache_geometry(num_kv_heads, head_size, block_size, num_blocks)) return rc;
+  if (new_token_stride < static_cast<int64_t>(num_kv_heads) * head_size)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  if (new_token_stride % 8 != 0) return B200ATTN_ERR_MISALIGNED;
+  p = ScatterParams{};
+  p.k_cache = static_cast<uint4*>(k_cache);
+  p.v_cache = static_cast<uint4*>(v_cache);
+  p.k_new = static_cast<const uint4*>(k_new);
+  p.v_new = static_cast<const uint4*>(v_new);
+  p.new_token_stride_v = new_token_stride / 8;
+  p.num_kv_heads = num_kv_heads;
+  p.block_size = block_size;
+  p.num_blocks = num_blocks;
+  return B200ATTN_OK;
+}
+
+template <int HD, int BS, int STAGES>
+static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p,
+                         int num_users, cudaStream_t s) {
+  using L = DecodeSmem<HD, BS, STAGES>;
+  auto kern = paged_decode_splitkv_kernel<HD, BS, STAGES>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid(p.num_splits, p.num_kv_heads, num_users);
+  kern<<<grid, kDecThreads, L::kTotalBytes, s>>>(tk, tv, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (p.num_splits > 1) {
+    dim3 cgrid(p.num_q_heads, num_users);
+    decode_combine_kernel<HD><<<cgrid, HD, 0, s>>>(p);
+    e = cudaGetLastError();
+  }
+  return static_cast<int>(e);
+}
+
+template <int HD, int BS>
+static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const PrefillParams& p, int total_tiles, cudaStream_t s) {
+  using L = PrefillSmem<HD>;
+  auto kern = prefill_tcgen05_kernel<HD, BS>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid(total_tiles, p.num_q_heads);
+  kern<<<grid, kPfThreads, L::kTotalBytes, s>>>(tq, tk, tv, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace b200attn
+
+using namespace b200attn;
+
+extern "C" {
+
+int b200attn_version(void) { return B200ATTN_VERSION; }
+
+const char* b200attn_status_string(int status) {
+  switch (status) {
+    case B200ATTN_OK: return "ok";
+    case B200ATTN_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case B200ATTN_ERR_UNSUPPORTED:
+      return "unsupported geometry (head_size must be 64 or 128, block_size 32 or 64, "
+             "q heads per kv head <= 16 for decode)";
+    case B200ATTN_ERR_MISALIGNED: return "pointer or stride is not 16-byte aligned";
+    case B200ATTN_ERR_WORKSPACE: return "decode workspace missing or too small";
+    case B200ATTN_ERR_BAD_ARGUMENT: return "bad argument (negative size or inconsistent head counts)";
+    case B200ATTN_ERR_NO_DEVICE: return "no usable CUDA device (this library has no CPU path)";
+    case B200ATTN_ERR_TENSOR_MAP: return "the driver refused the TMA tensor map for this layout";
+    case B200ATTN_ERR_TOO_LARGE: return "size beyond the supported maximum";
+    default:
+      if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+      return "unknown status";
+  }
+}
+
+int b200attn_paged_update_cache(void* k_cache, void* v_cache, const void* k_new,
+                                const void* v_new, int64_t new_token_stride,
+                                const int32_t* update_indices, const int32_t* page_table,
+                                int64_t page_table_stride, int page_table_width, int num_users,
+                                int num_kv_heads, int head_size, int block_size,
+                                int64_t num_blocks, void* stream) {
+  if (num_users < 0 || page_table_width <= 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (!update_indices || !page_table) return B200ATTN_ERR_NULL_POINTER;
+  ScatterParams p;
+  if (int rc = fill_scatter_common(p, k_cache, v_cache, k_new, v_new, new_token_stride,
+                                   num_kv_heads, head_size, block_size, num_blocks))
+    return rc;
+  p.positions = update_indices;
+  p.page_table = page_table;
+  p.page_table_stride = page_table_stride;
+  p.page_table_width = page_table_width;
+  p.num_tokens = num_users;
+  return launch_scatter(kScatterUpdate, p, head_size, stream);
+}
+
+int b200attn_paged_fill_cache(void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                              int64_t new_token_stride, const int32_t* fill_page_table,
+                              int64_t page_table_stride, int page_table_width,
+                              const int32_t* batch_idx, int num_users, int tokens_per_user,
+                              int num_kv_heads, int head_size, int block_size,
+                              int64_t num_blocks, void* stream) {
+  if (num_users < 0 || tokens_per_user < 0 || page_table_width <= 0)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  if (!fill_page_table) return B200ATTN_ERR_NULL_POINTER;
+  if ((static_cast<int64_t>(tokens_per_user) + block_size - 1) / block_size > page_table_width)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  ScatterParams p;
+  if (int rc = fill_scatter_common(p, k_cache, v_cache, k_new, v_new, new_token_stride,
+                                   num_kv_heads, head_size, block_size, num_blocks))
+    return rc;
+  p.page_table = fill_page_table;
+  p.page_table_stride = page_table_stride;
+  p.page_table_width = page_table_width;
+  p.batch_idx = batch_idx;
+  p.tokens_per_user = tokens_per_user > 0 ? tokens_per_user : 1;
+  p.num_tokens = static_cast<int64_t>(num_users) * tokens_per_user;
+  return launch_scatter(kScatterFill, p, head_size, stream);
+}
+
+int b200attn_kv_scatter_slots(void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                              int64_t new_token_stride, const int64_t* slot_mapping,
+                              int num_tokens, int num_kv_heads, int head_size, int block_size,
+                              int64_t num_blocks, void* stream) {
+  if (num_tokens < 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (!slot_mapping) return B200ATTN_ERR_NULL_POINTER;
+  ScatterParams p;
+  if (int rc = fill_scatter_common(p, k_cache, v_cache, k_new, v_new, new_token_stride,
+                                   num_kv_heads, head_size, block_size, num_blocks))
+    return rc;
+  p.slot_mapping = slot_mapping;
+  p.num_tokens = num_tokens;
+  return launch_scatter(kScatterSlots, p, head_size, stream);
+}
+
+// -------------------------------------------------------------------------------- decode
+int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int block_size,
+                                int max_context_len) {
+  (void)block_size;
+  if (num_users <= 0 || num_kv_heads <= 0 || max_context_len <= 0) return 1;
+  int sm = 148;
+  DeviceInfo* dev;
+  if (get_device(&dev) == B200ATTN_OK) sm = dev->sm_count;
+  const int64_t slots = static_cast<int64_t>(sm) * 2;  // two CTAs per SM
+  const int64_t tiles = (max_context_len + kDecTile - 1) / kDecTile;
+  const int64_t total_tiles = tiles * num_users * num_kv_heads;
+  // Chunks small enough that ~16 of them pass through every CTA slot (short tail, balanced
+  // ragged batches) but never below 4 tiles (pipeline fill and combine cost).
+  int64_t chunk = total_tiles / (slots * 16);
+  if (chunk < 4) chunk = 4;
+  int64_t splits = (tiles + chunk - 1) / chunk;
+  if (splits < 1) splits = 1;
+  if (splits > 128) splits = 128;
+  return static_cast<int>(splits);
+}
+
+size_t b200attn_decode_workspace_bytes(int num_users, int num_q_heads, int head_size,
+                                       int num_splits) {
+  if (num_splits <= 1 || num_users <= 0 || num_q_heads <= 0 || head_size <= 0) return 0;
+  const size_t rows = static_cast<size_t>(num_users) * num_q_heads * num_splits;
+  size_t o_bytes = rows * head_size * sizeof(float);
+  o_bytes = (o_bytes + 255) & ~static_cast<size_t>(255);
+  return o_bytes + rows * sizeof(float2);
+}
+
+
+int b200attn_paged_decode(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
+                          const void* k_cache, const void* v_cache, const int32_t* page_table,
+                          int64_t page_table_stride, int page_table_width, const int32_t* cur_pos,
+                          int num_users, int num_q_heads, int num_kv_heads, int head_size,
+                          int block_size, int64_t num_blocks, float scale, int max_context_len,
+                          int num_splits, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!out || !q || !k_cache || !v_cache || !page_table || !cur_pos)
+    return B200ATTN_ERR_NULL_POINTER;
+  if (num_users < 0 || num_q_heads <= 0 || page_table_width <= 0 || num_splits < 0)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  if (int rc = check_cache_geometry(num_kv_heads, head_size, block_size, num_blocks)) return rc;
+  if (num_q_heads % num_kv_heads != 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  const int group = num_q_heads / num_kv_heads;
+  if (group > 16) return B200ATTN_ERR_UNSUPPORTED;
+  if (!aligned16(out) || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) ||
+      q_row_stride % 8 != 0 || out_row_stride % 8 != 0)
+    return B200ATTN_ERR_MISALIGNED;
+  if (q_row_stride < static_cast<int64_t>(num_q_heads) * head_size ||
+      out_row_stride < static_cast<int64_t>(num_q_heads) * head_size)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (num_users == 0) return B200ATTN_OK;
+  if (num_users > 65535 || num_kv_heads > 65535) return B200ATTN_ERR_TOO_LARGE;
+
+  if (max_context_len <= 0) max_context_len = page_table_width * block_size;
+  if (num_splits == 0)
+    num_splits = b200attn_decode_auto_splits(num_users, num_kv_heads, block_size, max_context_len);
+  const size_t need = b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits);
+  if (num_splits > 1 && (!workspace || workspace_bytes < need || !aligned16(workspace)))
+    return B200ATTN_ERR_WORKSPACE;
+
+  CUtensorMap tk, tv;
+  const uint64_t rows = static_cast<uint64_t>(num_blocks) * num_kv_heads * block_size;
+  if (int rc = make_map(&tk, k_cache, rows, head_size, head_size, block_size)) return rc;
+  if (int rc = make_map(&tv, v_cache, rows, head_size, head_size, block_size)) return rc;
+
+  DecodeParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.q_row_stride = q_row_stride;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_row_stride = out_row_stride;
+  p.page_table = page_table;
+  p.page_table_stride = page_table_stride;
+  p.page_table_width = page_table_width;
+  p.cur_pos = cur_pos;
+  p.num_q_heads = num_q_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.group = group;
+  p.num_splits = num_splits;
+  p.num_blocks = num_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err_word = dev->err_word;
+  if (num_splits > 1) {
+    const size_t rows_p = static_cast<size_t>(num_users) * num_q_heads * num_splits;
+    size_t o_bytes = rows_p * head_size * sizeof(float);
+    o_bytes = (o_bytes + 255) & ~static_cast<size_t>(255);
+    p.part_o = static_cast<float*>(workspace);
+    p.part_ml = reinterpret_cast<float2*>(static_cast<uint8_t*>(workspace) + o_bytes);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_size == 128 && block_size == 64) return launch_decode<128, 64, 3>(tk, tv, p, num_users, s);
+  if (head_size == 128 && block_size == 32) return launch_decode<128, 32, 3>(tk, tv, p, num_users, s);
+  if (head_size == 64 && block_size == 64) return launch_decode<64, 64, 4>(tk, tv, p, num_users, s);
+  return launch_decode<64, 32, 4>(tk, tv, p, num_users, s);
+}
+
+// ------------------------------------------------------------------------------- prefill
+
+int b200attn_prefill(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
+                     const void* k_src, const void* v_src, int kv_is_paged,
+                     int64_t kv_token_stride, const int32_t* page_table,
+                     int64_t page_table_stride, int page_table_width, const int32_t* cu_q,
+                     const int32_t* cu_q_host, const int32_t* q_start, int num_seqs, int total_q,
+                     int num_q_heads, int num_kv_heads, int head_size, int block_size,
+                     int64_t num_blocks, float scale, void* stream) {
+  if (!out || !q || !k_src || !v_src || !cu_q || !cu_q_host) return B200ATTN_ERR_NULL_POINTER;
+  if (num_seqs < 0 || total_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  if (num_q_heads % num_kv_heads != 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (head_size != 64 && head_size != 128) return B200ATTN_ERR_UNSUPPORTED;
+  if (!aligned16(out) || !aligned16(q) || !aligned16(k_src) || !aligned16(v_src) ||
+      q_row_stride % 8 != 0 || out_row_stride % 8 != 0)
+    return B200ATTN_ERR_MISALIGNED;
+  if (q_row_stride < static_cast<int64_t>(num_q_heads) * head_size ||
+      out_row_stride < static_cast<int64_t>(num_q_heads) * head_size)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  if (kv_is_paged) {
+    if (!page_table || page_table_width <= 0) return B200ATTN_ERR_NULL_POINTER;
+    if (int rc = check_cache_geometry(num_kv_heads, head_size, block_size, num_blocks)) return rc;
+  } else {
+    if (q_start) return B200ATTN_ERR_BAD_ARGUMENT;
+    if (kv_token_stride % 8 != 0) return B200ATTN_ERR_MISALIGNED;
+    if (kv_token_stride < static_cast<int64_t>(num_kv_heads) * head_size)
+      return B200ATTN_ERR_BAD_ARGUMENT;
+    if (block_size != 32 && block_size != 64) block_size = 64;  // unused by this form
+  }
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (num_seqs == 0 || total_q == 0) return B200ATTN_OK;
+
+  int total_tiles = 0;
+  for (int s = 0; s < num_seqs; ++s) {
+    const int len = cu_q_host[s + 1] - cu_q_host[s];
+    if (len < 0) return B200ATTN_ERR_BAD_ARGUMENT;
+    total_tiles += (len + kPfM - 1) / kPfM;
+  }
+  if (cu_q_host[num_seqs] - cu_q_host[0] > total_q) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (total_tiles == 0) return B200ATTN_OK;
+  if (num_q_heads > 65535) return B200ATTN_ERR_TOO_LARGE;
+
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_map(&tq, q, total_q, static_cast<uint64_t>(num_q_heads) * head_size,
+                        q_row_stride, kPfM))
+    return rc;
+  if (kv_is_paged) {
+    const uint64_t rows = static_cast<uint64_t>(num_blocks) * num_kv_heads * block_size;
+    if (int rc = make_map(&tk, k_src, rows, head_size, head_size, block_size)) return rc;
+    if (int rc = make_map(&tv, v_src, rows, head_size, head_size, block_size)) return rc;
+  } else {
+    const uint64_t cols = static_cast<uint64_t>(num_kv_heads) * head_size;
+    if (int rc = make_map(&tk, k_src, total_q, cols, kv_token_stride, kPfN)) return rc;
+    if (int rc = make_map(&tv, v_src, total_q, cols, kv_token_stride, kPfN)) return rc;
+  }
+
+  PrefillParams p{};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_row_stride = out_row_stride;
+  p.page_table = page_table;
+  p.page_table_stride = page_table_stride;
+  p.page_table_width = page_table_width;
+  p.cu_q = cu_q;
+  p.q_start = q_start;
+  p.num_seqs = num_seqs;
+  p.num_q_heads = num_q_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.group = num_q_heads / num_kv_heads;
+  p.kv_is_paged = kv_is_paged ? 1 : 0;
+  p.num_blocks = num_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err_word = dev->err_word;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_size == 128 && block_size == 64) return launch_prefill<128, 64>(tq, tk, tv, p, total_tiles, s);
+  if (head_size == 128) return launch_prefill<128, 32>(tq, tk, tv, p, total_tiles, s);
+  if (block_size == 64) return launch_prefill<64, 64>(tq, tk, tv, p, total_tiles, s);
+  return launch_prefill<64, 32>(tq, tk, tv, p, total_tiles, s);
+}
+
+int b200attn_read_error_word(int32_t* out_host, void* stream) {
+  if (!out_host) return B200ATTN_ERR_NULL_POINTER;
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(out_host, dev->err_word, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(dev->err_word, 0, sizeof(int), s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  return static_cast<int>(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,387 @@
+// Paged GQA decode attention: split-KV streaming kernel + split combine.
+//
+// Grid (split, kv_head, user).  One CTA owns one KV head of one user and the G = nq/nkv
+// query heads that share it, so every K/V byte is read from HBM once.  A producer warp walks
+// the user's page-table slice and pulls one 64-token tile of K and V per stage into a
+// shared-memory ring with TMA (128-byte swizzled boxes of [block_size x 64] elements, one
+// mbarrier per stage).  Four consumer warps each take 16 tokens of the tile:
+// S = Q.K^T and O += P.V run on mma.sync m16n8k16 with the G query rows padded to 16 (the
+// kernel is HBM-bound; tensor throughput is irrelevant), the softmax is the online
+// (running max / running sum) form in fp32 with warp-shuffle row reductions.  The four
+// warps' partial (m, l, O) are merged through shared memory at the end, and the CTA writes
+// either the final bf16 rows (one split) or an fp32 partial that the combine kernel merges.
+#pragma once
+#include "ptx.cuh"
+
+namespace b200attn {
+
+constexpr int kDecTile = 64;           // tokens per pipeline stage
+constexpr int kDecConsumerWarps = 4;   // 16 tokens each
+constexpr int kDecThreads = (kDecConsumerWarps + 1) * 32;
+
+struct DecodeParams {
+  const __nv_bfloat16* q;
+  int64_t q_row_stride;
+  __nv_bfloat16* out;
+  int64_t out_row_stride;
+  const int32_t* page_table;
+  int64_t page_table_stride;
+  int page_table_width;
+  const int32_t* cur_pos;
+  float* part_o;    // [users, nq, splits, hd]
+  float2* part_ml;  // [users, nq, splits]  (running max in log2 units, running sum)
+  int num_q_heads;
+  int num_kv_heads;
+  int group;        // nq / nkv
+  int num_splits;
+  int64_t num_blocks;
+  float scale_log2; // softmax scale * log2(e)
+  int* err_word;
+};
+
+template <int HD, int BS, int STAGES>
+struct DecodeSmem {
+  static constexpr int kSub = HD / 64;                 // 64-element (128 B) column groups
+  static constexpr int kPages = kDecTile / BS;         // pages per tile
+  static constexpr int kBoxBytes = BS * 128;           // one TMA box
+  static constexpr int kTensorBytes = kPages * kSub * kBoxBytes;  // K (or V) of one tile
+  static constexpr int kStageBytes = 2 * kTensorBytes;
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  static constexpr int kBarrierBytes = 2 * STAGES * 8 + 16;
+  static constexpr int kTotalBytes = kRingBytes + kBarrierBytes + 1024;  // 1 KiB alignment slack
+};
+
+template <int HD, int BS, int STAGES>
+__global__ void __launch_bounds__(kDecThreads)
+paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
+                            const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
+  using L = DecodeSmem<HD, BS, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + L::kRingBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + STAGES);
+
+  // A CTA of this launch already gave up on a wait: do not repeat the timeout per CTA.
+  if (*reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout) return;
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int user = blockIdx.z;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int ctx = p.cur_pos[user] + 1;  // keys 0 .. cur_pos
+  const int n_tiles = ctx > 0 ? (ctx + kDecTile - 1) / kDecTile : 0;
+  const int tiles_per_split = (n_tiles + p.num_splits - 1) / p.num_splits;
+  const int t_begin = split * tiles_per_split;
+  const int t_end = min(n_tiles, t_begin + tiles_per_split);
+  const int G = p.group;
+
+  if (t_begin >= t_end) {
+    // Nothing for this split: publish an empty partial (or zeros when it is the only split).
+    if (p.num_splits > 1) {
+      if (threadIdx.x < G) {
+        const int64_t row = (static_cast<int64_t>(user) * p.num_q_heads + kvh * G + threadIdx.x) *
+                                p.num_splits + split;
+        p.part_ml[row] = make_float2(-INFINITY, 0.f);
+      }
+    } else {
+      for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int r = i / HD, d = i - r * HD;
+        p.out[static_cast<int64_t>(user) * p.out_row_stride + (kvh * G + r) * HD + d] =
+            __float2bfloat16(0.f);
+      }
+    }
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kDecConsumerWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kDecConsumerWarps) {
+    // ------------------------------------------------------------------ producer warp
+    if (lane == 0) {
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
+    }
+    const uint64_t policy = l2_policy_evict_first();
+    const int n_pages = (ctx + BS - 1) / BS;
+    const int32_t* pt = p.page_table + static_cast<int64_t>(user) * p.page_table_stride;
+    const int first_page = t_begin * L::kPages;
+    // Each lane keeps one page id of a 32-page window; the next window is fetched early.
+    int win_base = first_page;
+    auto fetch = [&](int base) {
+      // pages past the end repeat the last one
+      const int idx = min(min(base + lane, n_pages - 1), p.page_table_width - 1);
+      return pt[idx];
+    };
+    int cur_ids = fetch(win_base);
+    int nxt_ids = fetch(win_base + 32);
+    for (int t = t_begin; t < t_end; ++t) {
+      const int it = t - t_begin;
+      const int stage = it % STAGES;
+      const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+      mbar_wait(&empty_bar[stage], parity, abort_flag, p.err_word);
+      uint8_t* kdst = ring + stage * L::kStageBytes;
+      uint8_t* vdst = kdst + L::kTensorBytes;
+      if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+#pragma unroll
+      for (int pg = 0; pg < L::kPages; ++pg) {
+        const int page_idx = t * L::kPages + pg;
+        if (page_idx - win_base >= 32) {
+          win_base += 32;
+          cur_ids = nxt_ids;
+          nxt_ids = fetch(win_base + 32);
+        }
+        int64_t blk = __shfl_sync(0xffffffffu, cur_ids, page_idx - win_base);
+        if (blk < 0 || blk >= p.num_blocks) {
+          if (lane == 0) atomicExch(p.err_word, kDevBadIndex);
+          blk = 0;
+        }
+        if (lane == 0) {
+          const int32_t y = static_cast<int32_t>((blk * p.num_kv_heads + kvh) * BS);
+#pragma unroll
+          for (int s = 0; s < L::kSub; ++s) {
+            tma_load_2d(kdst + (pg * L::kSub + s) * L::kBoxBytes, &tm_k, &full_bar[stage], s * 64,
+                        y, policy);
+            tma_load_2d(vdst + (pg * L::kSub + s) * L::kBoxBytes, &tm_v, &full_bar[stage], s * 64,
+                        y, policy);
+          }
+        }
+      }
+    }
+    return;  // consumers wait on every full barrier, so no copy is in flight at kernel end
+  }
+
+  // -------------------------------------------------------------------- consumer warps
+  const int g = lane >> 2;   // fragment row (query head within the group); g + 8 is the second row
+  const int tq = lane & 3;
+
+  // Q fragments: A operand rows = query heads of this KV head (rows >= G are zero).
+  uint32_t qf[HD / 16][4];
+  {
+    const __nv_bfloat16* qrow = p.q + static_cast<int64_t>(user) * p.q_row_stride +
+                                static_cast<int64_t>(kvh) * G * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const int d0 = ks * 16 + tq * 2;
+      const uint32_t lo0 = (g < G) ? *reinterpret_cast<const uint32_t*>(qrow + g * HD + d0) : 0u;
+      const uint32_t lo8 = (g < G) ? *reinterpret_cast<const uint32_t*>(qrow + g * HD + d0 + 8) : 0u;
+      const uint32_t hi0 =
+          (g + 8 < G) ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * HD + d0) : 0u;
+      const uint32_t hi8 =
+          (g + 8 < G) ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * HD + d0 + 8) : 0u;
+      qf[ks][0] = lo0;
+      qf[ks][1] = hi0;
+      qf[ks][2] = lo8;
+      qf[ks][3] = hi8;
+    }
+  }
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY;  // running max, rows g and g+8 (log2 units)
+  float l_lo = 0.f, l_hi = 0.f;              // running sum (this thread's share of the row)
+
+  // Per-lane ldmatrix row addressing inside a tile.
+  //   K (non-transposed): matrix m = lane/8 -> n-tile m/2, k-half m%2; row = token.
+  //   V (transposed):     matrix m = lane/8 -> token half m%2, d-tile offset m/2.
+  const int lm = lane >> 3, lr = lane & 7;
+  const int k_tok = warp * 16 + (lm >> 1) * 8 + lr;
+  const int v_tok = warp * 16 + (lm & 1) * 8 + lr;
+  const int k_page = k_tok / BS, k_row = k_tok % BS;
+  const int v_page = v_tok / BS, v_row = v_tok % BS;
+
+  for (int t = t_begin; t < t_end; ++t) {
+    const int it = t - t_begin;
+    const int stage = it % STAGES;
+    mbar_wait(&full_bar[stage], (it / STAGES) & 1, abort_flag, p.err_word);
+    const uint32_t kbase = smem_u32(ring + stage * L::kStageBytes);
+    const uint32_t vbase = kbase + L::kTensorBytes;
+    const int tok0 = t * kDecTile + warp * 16;   // first token of this warp's slice
+
+    if (tok0 < ctx) {
+      const bool tail = (tok0 + 16 > ctx);
+      if (tail) {
+        // Zero this warp's V rows past the context so that stale or non-finite cache
+        // contents cannot reach the accumulator through 0 * x.
+        for (int i = lane; i < 16 * (HD / 8); i += 32) {
+          const int r = i / (HD / 8), c = i % (HD / 8);
+          const int tok = warp * 16 + r;
+          if (t * kDecTile + tok >= ctx) {
+            const int pg = tok / BS, row = tok % BS;
+            const uint32_t a = vbase + ((pg * L::kSub + (c >> 3)) * BS + row) * 128 +
+                               (((c & 7) ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
+          }
+        }
+        fence_proxy_async_smem();  // the next TMA write to this stage follows generic writes
+        __syncwarp();
+      }
+
+      // ---- S = Q K^T for 16 tokens (two 8-token n-tiles)
+      float s[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const int cc = ks * 2 + (lm & 1);  // 16-byte chunk along head_size
+        const uint32_t a = kbase + ((k_page * L::kSub + (cc >> 3)) * BS + k_row) * 128 +
+                           (((cc & 7) ^ (k_row & 7)) << 4);
+        uint32_t b[4];
+        ldmatrix_x4(b, a);
+        mma_bf16_16816(s[0], qf[ks], b[0], b[1]);
+        mma_bf16_16816(s[1], qf[ks], b[2], b[3]);
+      }
+
+      // ---- online softmax (log2 domain)
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] *= p.scale_log2;
+      if (tail) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int tok = tok0 + i * 8 + tq * 2 + (j & 1);
+            if (tok >= ctx) s[i][j] = -INFINITY;
+          }
+      }
+      float mx_lo = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+      float mx_hi = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      // tok0 < ctx guarantees at least one unmasked key, so mn_* is finite here.
+      const float c_lo = fast_exp2(m_lo - mn_lo), c_hi = fast_exp2(m_hi - mn_hi);
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+      float pr[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        pr[i][0] = fast_exp2(s[i][0] - mn_lo);
+        pr[i][1] = fast_exp2(s[i][1] - mn_lo);
+        pr[i][2] = fast_exp2(s[i][2] - mn_hi);
+        pr[i][3] = fast_exp2(s[i][3] - mn_hi);
+      }
+      l_lo = l_lo * c_lo + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
+      l_hi = l_hi * c_hi + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
+      if (__any_sync(0xffffffffu, (c_lo != 1.f) || (c_hi != 1.f))) {
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+          o[i][0] *= c_lo;
+          o[i][1] *= c_lo;
+          o[i][2] *= c_hi;
+          o[i][3] *= c_hi;
+        }
+      }
+      uint32_t pa[4];
+      pa[0] = pack_bf16x2(pr[0][0], pr[0][1]);
+      pa[1] = pack_bf16x2(pr[0][2], pr[0][3]);
+      pa[2] = pack_bf16x2(pr[1][0], pr[1][1]);
+      pa[3] = pack_bf16x2(pr[1][2], pr[1][3]);
+
+      // ---- O += P V  (k = this warp's 16 tokens, n = head_size)
+#pragma unroll
+      for (int dn = 0; dn < HD / 8; dn += 2) {
+        const int cc = dn + (lm >> 1);
+        const uint32_t a = vbase + ((v_page * L::kSub + (cc >> 3)) * BS + v_row) * 128 +
+                           (((cc & 7) ^ (v_row & 7)) << 4);
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, a);
+        mma_bf16_16816(o[dn], pa, b[0], b[1]);
+        mma_bf16_16816(o[dn + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[stage]);
+  }
+
+  // -------------------------------------------------------------------- merge the 4 warps
+  // Row sums: finish the quad reduction.
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+  // All consumer warps are past their last full-barrier wait: the ring is free to reuse.
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32));
+  float* mo = reinterpret_cast<float*>(ring);                       // [4 warps][16 rows][HD]
+  float* mm = mo + kDecConsumerWarps * 16 * HD;                     // [4][16] max
+  float* ml = mm + kDecConsumerWarps * 16;                          // [4][16] sum
+  static_assert((kDecConsumerWarps * 16 * (HD + 2)) * 4 <= L::kRingBytes, "merge scratch fits");
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) {
+    const int d = i * 8 + tq * 2;
+    *reinterpret_cast<float2*>(mo + (warp * 16 + g) * HD + d) = make_float2(o[i][0], o[i][1]);
+    *reinterpret_cast<float2*>(mo + (warp * 16 + g + 8) * HD + d) = make_float2(o[i][2], o[i][3]);
+  }
+  if (tq == 0) {
+    mm[warp * 16 + g] = m_lo;
+    mm[warp * 16 + g + 8] = m_hi;
+    ml[warp * 16 + g] = l_lo;
+    ml[warp * 16 + g + 8] = l_hi;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32));
+
+  for (int i = threadIdx.x; i < G * HD; i += kDecConsumerWarps * 32) {
+    const int r = i / HD, d = i - r * HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecConsumerWarps; ++w) m = fmaxf(m, mm[w * 16 + r]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecConsumerWarps; ++w) {
+      const float mw = mm[w * 16 + r];
+      const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+      acc += f * mo[(w * 16 + r) * HD + d];
+      l += f * ml[w * 16 + r];
+    }
+    const int head = kvh * G + r;
+    if (p.num_splits == 1) {
+      p.out[static_cast<int64_t>(user) * p.out_row_stride + head * HD + d] =
+          __float2bfloat16(l > 0.f ? acc / l : 0.f);
+    } else {
+      const int64_t row =
+          (static_cast<int64_t>(user) * p.num_q_heads + head) * p.num_splits + split;
+      p.part_o[row * HD + d] = acc;
+      if (d == 0) p.part_ml[row] = make_float2(m, l);
+    }
+  }
+}
+
+// Merges the split partials of one (user, q head) row and writes bf16.
+template <int HD>
+__global__ void __launch_bounds__(HD) decode_combine_kernel(const DecodeParams p) {
+  const int head = blockIdx.x;
+  const int user = blockIdx.y;
+  const int d = threadIdx.x;
+  const int64_t row0 = (static_cast<int64_t>(user) * p.num_q_heads + head) * p.num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, p.part_ml[row0 + s].x);
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < p.num_splits; ++s) {
+    const float2 ml = p.part_ml[row0 + s];
+    if (ml.x == -INFINITY) continue;
+    const float f = fast_exp2(ml.x - m);
+    acc += f * p.part_o[(row0 + s) * HD + d];
+    l += f * ml.y;
+  }
+  p.out[static_cast<int64_t>(user) * p.out_row_stride + head * HD + d] =
+      __float2bfloat16(l > 0.f ? acc / l : 0.f);
+}
+
+}  // namespace b200attn
