@@ -1,0 +1,499 @@
+#!/usr/bin/env python
+"""Benchmark of the attention + KV-cache hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload ...]
+
+Default workload ("c4"): long-context paged GQA decode with Llama-3.1-70B attention shapes
+(64 q heads, 8 kv heads, head_dim 128, bf16, batch 32, every context 32768 tokens, block 64),
+KV heads sharded across the N GPUs with no data-path collective.  One step = one decode pass of
+the hot path over the batch: the KV write of the new token (1 launch) and the split-KV decode
+attention (2 launches).  The headline value is decode-attention HBM GB/s: algorithmic bytes of
+the batch divided by the step time (max over ranks).
+
+One JSON line is printed by rank 0.  Besides the contract keys it carries
+  roofline      the decode call (split-KV kernel + combine) against the measured HBM peak,
+  cpu_baseline  the CPU oracle port timed on a bounded sample on this machine's cores (N=1),
+  e2e           the same metric through B200AttentionBackendImpl.forward with pinned HOST inputs
+                copied in and the output copied back every step (the KV cache is the runner's
+                resident state, as in the plugin),
+  prefill       the config-2 causal prefill (tcgen05 kernel) in TFLOP/s against the tensor peak.
+`--impl reference` times the reference algorithm's CPU path (the oracle port; the Python
+reference tree itself is not present on the GPU machine) on a bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "tt-xla_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+WORKLOADS = {
+    # name: decode geometry
+    "c4": dict(nq=64, nkv=8, hd=128, bs=64, users=32, ctx_lo=32768, ctx_hi=32768,
+               desc="c4_long_context_decode_llama70b_B32_L32768"),
+    "c3": dict(nq=32, nkv=8, hd=128, bs=64, users=64, ctx_lo=1024, ctx_hi=8192,
+               desc="c3_decode_rows_llama8b_B64_L1024-8192"),
+    "c1": dict(nq=32, nkv=8, hd=64, bs=32, users=8, ctx_lo=128, ctx_hi=1024,
+               desc="c1_decode_llama1b_B8_L128-1024"),
+}
+
+
+# ------------------------------------------------------------------------------ helpers
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    source="measured")
+    except Exception:
+        return dict(hbm_gbs=FALLBACK_HBM_GBS, bf16_tflops=FALLBACK_BF16_TFLOPS, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons in the background during the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def decode_algorithmic_bytes(ctx_lens: torch.Tensor, nq: int, nkv: int, hd: int, bs: int) -> int:
+    """K and V rows of every context read once (the G query heads of a KV head share them),
+    q read and o written, page-table entries and positions read."""
+    users = ctx_lens.numel()
+    kv = int(ctx_lens.sum()) * 2 * nkv * hd * 2
+    qo = 2 * users * nq * hd * 2
+    meta = int(((ctx_lens + bs - 1) // bs).sum()) * 4 + 4 * users
+    return kv + qo + meta
+
+
+def gen_cache(nb: int, nkv: int, bs: int, hd: int, seed: int, device) -> torch.Tensor:
+    """N(0,1) cache generated block-range by block-range so the fp32 temporaries stay small."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    out = torch.empty((nb, nkv, bs, hd), dtype=torch.bfloat16, device=device)
+    step = max(1, (256 << 20) // (nkv * bs * hd * 4))
+    for b0 in range(0, nb, step):
+        b1 = min(nb, b0 + step)
+        out[b0:b1] = torch.randn((b1 - b0, nkv, bs, hd), generator=g, device=device,
+                                 dtype=torch.float32).to(torch.bfloat16)
+    return out
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and not dist.is_initialized():
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world: int):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ------------------------------------------------------------------------------ workloads
+def make_decode_workload(wl: dict, rank: int, world: int, device):
+    """Per-rank tensors of the decode workload: this rank's KV heads of every block, its q heads,
+    and a replica of the int32 metadata."""
+    nq, nkv, hd, bs, users = wl["nq"], wl["nkv"], wl["hd"], wl["bs"], wl["users"]
+    if nkv % world != 0:
+        raise SystemExit(f"{nkv} kv heads do not shard over {world} GPUs")
+    g = torch.Generator().manual_seed(4)
+    ctx = torch.randint(wl["ctx_lo"], wl["ctx_hi"] + 1, (users,), generator=g)
+    nblk = (wl["ctx_hi"] + bs - 1) // bs
+    nb = users * nblk
+    page_table = torch.randperm(nb, generator=g).reshape(users, nblk).to(torch.int32)
+    nkv_l, nq_l = nkv // world, nq // world
+    k_cache = gen_cache(nb, nkv_l, bs, hd, 100 + rank, device)
+    v_cache = gen_cache(nb, nkv_l, bs, hd, 200 + rank, device)
+    gq = torch.Generator().manual_seed(300 + rank)
+    host = dict(
+        q=torch.randn(users, nq_l * hd, generator=gq).to(torch.bfloat16).pin_memory(),
+        k=torch.randn(users, nkv_l * hd, generator=gq).to(torch.bfloat16).pin_memory(),
+        v=torch.randn(users, nkv_l * hd, generator=gq).to(torch.bfloat16).pin_memory(),
+        cache_position=(ctx - 1).to(torch.int32).pin_memory(),
+        page_table=page_table.pin_memory(),
+        out=torch.empty(users, nq_l * hd, dtype=torch.bfloat16).pin_memory(),
+    )
+    return dict(nq=nq_l, nkv=nkv_l, hd=hd, bs=bs, users=users, ctx=ctx, nb=nb,
+                k_cache=k_cache, v_cache=v_cache, host=host, max_ctx=int(ctx.max()))
+
+
+def run_decode_bench(args, wl, rank, world, device):
+    from b200attn import B200AttentionBackendImpl, B200Metadata, ops
+
+    w = make_decode_workload(wl, rank, world, device)
+    users, nq, nkv, hd, bs = w["users"], w["nq"], w["nkv"], w["hd"], w["bs"]
+    h = w["host"]
+    dev = {k: v.to(device) for k, v in h.items() if k != "out"}
+    out = torch.empty(users, nq * hd, dtype=torch.bfloat16, device=device)
+    q3 = dev["q"].view(users, nq, hd)
+    k3 = dev["k"].view(users, nkv, hd)
+    v3 = dev["v"].view(users, nkv, hd)
+    out3 = out.view(users, nq, hd)
+    scale = hd ** -0.5
+    splits = ops.decode_auto_splits(users, nkv, bs, w["max_ctx"])
+
+    def step():
+        ops.paged_update_cache(w["k_cache"], w["v_cache"], k3, v3, dev["cache_position"],
+                               dev["page_table"])
+        ops.paged_decode(q3, w["k_cache"], w["v_cache"], dev["page_table"], dev["cache_position"],
+                         scale=scale, out=out3, num_splits=splits, max_context_len=w["max_ctx"])
+
+    ops.read_error_word()
+    for _ in range(args.warmup):
+        step()
+    # ---- timed region: K steps, device events, max over ranks; per-step decode-call events too
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(args.steps)]
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    barrier(world)
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    barrier(world)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.steps):
+        ops.paged_update_cache(w["k_cache"], w["v_cache"], k3, v3, dev["cache_position"],
+                               dev["page_table"])
+        ev[i][0].record()
+        ops.paged_decode(q3, w["k_cache"], w["v_cache"], dev["page_table"], dev["cache_position"],
+                         scale=scale, out=out3, num_splits=splits, max_context_len=w["max_ctx"])
+        ev[i][1].record()
+    t1.record()
+    barrier(world)
+    clocks = sampler.stop() if sampler else None
+    total_ms = max_over_ranks(t0.elapsed_time(t1), world, device)
+    decode_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
+    decode_ms = max_over_ranks(decode_ms, world, device)
+    err = ops.read_error_word()
+    if err:
+        raise SystemExit(f"a kernel reported device error {err}")
+
+    # ---- e2e: through the backend's forward with pinned host inputs, output read back
+    impl = B200AttentionBackendImpl(nq, hd, scale, nkv, None, None, "auto")
+    kv = [w["k_cache"], w["v_cache"]]
+    d_q = torch.empty_like(dev["q"])
+    d_k = torch.empty_like(dev["k"])
+    d_v = torch.empty_like(dev["v"])
+    d_pos = torch.empty_like(dev["cache_position"])
+    d_pt = torch.empty_like(dev["page_table"])
+    md = B200Metadata(cache_position=d_pos, page_table=d_pt, num_users=users,
+                      batch_idx=torch.arange(users, dtype=torch.int32, device=device),
+                      max_seq_len=w["max_ctx"])
+    h2d = sum(h[k].numel() * h[k].element_size() for k in ("q", "k", "v", "cache_position",
+                                                             "page_table"))
+    d2h = h["out"].numel() * h["out"].element_size()
+
+    def e2e_step():
+        d_q.copy_(h["q"], non_blocking=True)
+        d_k.copy_(h["k"], non_blocking=True)
+        d_v.copy_(h["v"], non_blocking=True)
+        d_pos.copy_(h["cache_position"], non_blocking=True)
+        d_pt.copy_(h["page_table"], non_blocking=True)
+        impl.forward(None, d_q, d_k, d_v, kv, md, output=out)
+        h["out"].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        e2e_step()
+    barrier(world)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, device) / args.steps
+
+    full_bytes = decode_algorithmic_bytes(w["ctx"], wl["nq"], wl["nkv"], hd, bs)
+    rank_bytes = decode_algorithmic_bytes(w["ctx"], nq, nkv, hd, bs)
+    ms_per_step = total_ms / args.steps
+    return dict(w=w, full_bytes=full_bytes, rank_bytes=rank_bytes, ms_per_step=ms_per_step,
+                decode_ms=decode_ms, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h, clocks=clocks,
+                splits=splits, launches=3 * args.steps)
+
+
+def run_prefill_bench(args, rank, world, device, peaks):
+    """Config 2: 4 x 2048 tokens, nq 32 / nkv 8 / hd 128, block 64, heads sharded over the ranks.
+    One step = paged_fill_cache + causal prefill attention on the fresh K/V."""
+    from b200attn import ops
+
+    users, T, nq, nkv, hd, bs = 4, 2048, 32 // world, 8 // world, 128, 64
+    if nkv == 0:
+        return None
+    g = torch.Generator(device=device).manual_seed(7 + rank)
+    q = torch.randn(users * T, nq, hd, generator=g, device=device).bfloat16()
+    k = torch.randn(users * T, nkv, hd, generator=g, device=device).bfloat16()
+    v = torch.randn(users * T, nkv, hd, generator=g, device=device).bfloat16()
+    nblk = T // bs
+    nb = users * nblk + 1
+    pt = (torch.randperm(nb - 1)[: users * nblk] + 1).reshape(users, nblk).int().to(device)
+    kc = torch.zeros(nb, nkv, bs, hd, dtype=torch.bfloat16, device=device)
+    vc = torch.zeros_like(kc)
+    out = torch.empty_like(q)
+    cu_host = torch.arange(users + 1, dtype=torch.int32) * T
+    cu_dev = cu_host.to(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    k4, v4 = k.view(users, T, nkv, hd), v.view(users, T, nkv, hd)
+    steps = max(3, min(args.steps, 20))
+    times = []
+    for i in range(3 + steps):
+        flush.zero_()  # 256 MiB write: evicts the 126 MB L2 between iterations
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        c = torch.cuda.Event(enable_timing=True)
+        a.record()
+        ops.paged_fill_cache(kc, vc, k4, v4, pt)
+        b.record()
+        ops.prefill(q, k, v, cu_host, scale=hd ** -0.5, out=out, cu_q=cu_dev)
+        c.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append((a.elapsed_time(b), b.elapsed_time(c)))
+    fill_ms = max_over_ranks(statistics.mean(t[0] for t in times), world, device)
+    attn_ms = max_over_ranks(statistics.mean(t[1] for t in times), world, device)
+    flops_full = 4 * hd * 32 * users * (T * (T + 1) // 2)
+    tflops = flops_full / (attn_ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"] * world
+    return {"workload": "c2_causal_prefill_llama8b_4x2048", "tflops": round(tflops, 1),
+            "attn_ms": round(attn_ms, 4), "fill_cache_ms": round(fill_ms, 4),
+            "flops": flops_full, "l2": "flushed between iterations",
+            "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": peak,
+                         "unit": "TFLOP/s", "frac": round(tflops / peak, 4),
+                         "peak_source": peaks["source"]}}
+
+
+# ------------------------------------------------------------------------------ CPU side
+def cpu_decode_sample(wl: dict, n_users: int, seed: int = 0):
+    """A bounded sample of the decode workload for the CPU oracle: n_users users of the batch,
+    all heads, native bf16 (the dtype the reference's CPU branch would compute in)."""
+    nq, nkv, hd, bs = wl["nq"], wl["nkv"], wl["hd"], wl["bs"]
+    g = torch.Generator().manual_seed(1000 + seed)
+    ctx = torch.randint(wl["ctx_lo"], wl["ctx_hi"] + 1, (n_users,), generator=g)
+    nblk = (wl["ctx_hi"] + bs - 1) // bs
+    nb = n_users * nblk
+    pt = torch.randperm(nb, generator=g).reshape(n_users, nblk).to(torch.int32)
+    kc = torch.randn(nb, nkv, bs, hd, generator=g).to(torch.bfloat16)
+    vc = torch.randn(nb, nkv, bs, hd, generator=g).to(torch.bfloat16)
+    q = torch.randn(1, n_users, nq, hd, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, n_users, nkv, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, n_users, nkv, hd, generator=g).to(torch.bfloat16)
+    return dict(ctx=ctx, pt=pt, kc=kc, vc=vc, q=q, k=k, v=v, pos=(ctx - 1).to(torch.int32))
+
+
+def cpu_decode_step(s, hd: int):
+    """The reference's decode step on CPU: two cache writes and the paged decode attention.
+    The functional full-cache clone of the reference's cache write is part of what it does."""
+    from oracle import restate
+
+    kc = restate.paged_update_cache(s["kc"], s["k"], s["pos"], s["pt"])
+    vc = restate.paged_update_cache(s["vc"], s["v"], s["pos"], s["pt"])
+    return restate.paged_sdpa_decode(s["q"], kc, vc, s["pt"], s["pos"], hd ** -0.5)
+
+
+def run_cpu_baseline(wl: dict, budget_s: float = 15.0, max_users: int = 16):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    users = 1
+    s = cpu_decode_sample(wl, users)
+    t0 = time.perf_counter()
+    cpu_decode_step(s, wl["hd"])
+    t1 = time.perf_counter() - t0
+    n = int(max(1, min(max_users, budget_s / max(t1, 1e-3))))
+    if n > 1:
+        s = cpu_decode_sample(wl, n)
+        t0 = time.perf_counter()
+        cpu_decode_step(s, wl["hd"])
+        t1 = time.perf_counter() - t0
+        users = n
+    nbytes = decode_algorithmic_bytes(s["ctx"], wl["nq"], wl["nkv"], wl["hd"], wl["bs"])
+    return {"value": round(nbytes / t1 / 1e9, 4), "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{users} of {wl['users']} users of the batch, all heads, native bf16, "
+                      f"cache write + decode attention, {t1:.2f} s"}
+
+
+def run_reference_arm(args, wl):
+    """The reference algorithm's CPU path (oracle port) on this machine's cores: every step is
+    one user of the batch through cache write + decode attention."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    s = cpu_decode_sample(wl, 1)
+    nbytes = decode_algorithmic_bytes(s["ctx"], wl["nq"], wl["nkv"], wl["hd"], wl["bs"])
+    for _ in range(args.warmup):
+        cpu_decode_step(s, wl["hd"])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_decode_step(s, wl["hd"])
+    dt = (time.perf_counter() - t0) / args.steps
+    val = round(nbytes / dt / 1e9, 4)
+    sample = f"1 of {wl['users']} users per step, all heads, native bf16, {dt:.2f} s per step"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl["desc"], "parallelism": "cpu host cores"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    wl = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, wl)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: b200attn has no CPU path")
+    rank, world, local = dist_setup(args.gpus)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    peaks = load_peaks()
+
+    r = run_decode_bench(args, wl, rank, world, device)
+    prefill = None if args.no_prefill else run_prefill_bench(args, rank, world, device, peaks)
+    w = r["w"]
+    del r["w"]
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        w = None
+        torch.cuda.empty_cache()
+        cpu = run_cpu_baseline(wl)
+
+    if rank == 0:
+        value = r["full_bytes"] / (r["ms_per_step"] * 1e-3) / 1e9
+        e2e = r["full_bytes"] / (r["e2e_ms"] * 1e-3) / 1e9
+        achieved = r["rank_bytes"] / (r["decode_ms"] * 1e-3) / 1e9
+        line = {
+            "metric": "decode_attn_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl["desc"], "parallelism": f"kv_head_shard{world}",
+                       "q_heads": wl["nq"], "kv_heads": wl["nkv"], "head_dim": wl["hd"],
+                       "block_size": wl["bs"], "batch": wl["users"],
+                       "context": [wl["ctx_lo"], wl["ctx_hi"]], "num_splits": r["splits"],
+                       "l2": "inputs larger than L2 (per-rank KV stream "
+                             f"{r['rank_bytes'] / 1e6:.0f} MB vs 126 MB)"},
+            "clocks": r["clocks"],
+            "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": r["h2d"] * world,
+                    "d2h_bytes_per_step": r["d2h"] * world, "ms_per_step": round(r["e2e_ms"], 4)},
+            "gpu_launches": r["launches"],
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                         "traffic": None, "peak_source": peaks["source"],
+                         "kernel": "paged_decode_splitkv_kernel + decode_combine_kernel",
+                         "ms_per_launch": round(r["decode_ms"], 4),
+                         "algorithmic_bytes_per_launch": r["rank_bytes"]},
+            "cpu_baseline": cpu,
+        }
+        if prefill:
+            line["prefill"] = prefill
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
