@@ -140,6 +140,38 @@ int b200attn_paged_decode(void* out, int64_t out_row_stride,
                           int max_context_len, int num_splits,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Paged GQA decode attention for callers that cannot allocate device memory.
+ * No counterpart in the reference: this entry point exists for hosts of this library that
+ * must not call cudaMalloc around it -- code running inside a region where allocation is
+ * forbidden or would synchronise the device (a serving loop with a frozen memory pool, a
+ * plugin loaded by a process that owns all device memory, a real-time path that may not take
+ * the allocator lock).  It computes exactly what b200attn_paged_decode computes, with the same
+ * arguments minus the workspace: the split-KV scratch lives in a fixed array inside the
+ * library image, B200ATTN_STATIC_WORKSPACE_BYTES per GPU, which every GPU that loads the
+ * library holds until the process exits.
+ *   - num_splits = 0 picks the usual split count, lowered if needed until the scratch fits;
+ *     an explicit num_splits whose scratch exceeds the array is rejected with
+ *     B200ATTN_ERR_TOO_LARGE (nothing is launched).
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress with that device current).  Make that first call outside any
+ *     stream capture.
+ *   - The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.
+ *     Nothing in it has to start at zero (every slot that is read was written by the same
+ *     call), but two calls that overlap on the GPU -- different streams, or one stream from
+ *     two threads without ordering -- race on it.  Serialise them.
+ * ------------------------------------------------------------------------------------------ */
+#define B200ATTN_STATIC_WORKSPACE_BYTES (16u << 20)
+int b200attn_paged_decode_static(void* out, int64_t out_row_stride,
+                                 const void* q, int64_t q_row_stride,
+                                 const void* k_cache, const void* v_cache,
+                                 const int32_t* page_table, int64_t page_table_stride,
+                                 int page_table_width, const int32_t* cur_pos,
+                                 int num_users, int num_q_heads, int num_kv_heads, int head_size,
+                                 int block_size, int64_t num_blocks, float scale,
+                                 int max_context_len, int num_splits, void* stream);
+
 /* Split count the library would pick for a decode batch (host heuristic, no device access
  * beyond the SM count).  max_context_len <= 0 means "unknown": the page-table width bounds it. */
 int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int block_size,

@@ -33,6 +33,11 @@ SIGNATURES = {
          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_int, c_void_p,
          c_size_t, c_void_p],
     ),
+    "b200attn_paged_decode_static": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_int, c_void_p],
+    ),
     "b200attn_decode_auto_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "b200attn_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200attn_prefill": (

@@ -15,6 +15,10 @@ namespace b200attn {
 
 __device__ int g_err_word = 0;
 
+// Split-KV scratch of b200attn_paged_decode_static.  In host code this name is only a handle
+// for cudaGetSymbolAddress; kernels get the device address looked up below.
+static __device__ __align__(256) unsigned char g_static_workspace[B200ATTN_STATIC_WORKSPACE_BYTES];
+
 constexpr int kMaxDevices = 64;
 
 struct DeviceInfo {
@@ -25,6 +29,7 @@ struct DeviceInfo {
 
 static std::mutex g_mutex;
 static DeviceInfo g_devices[kMaxDevices];
+static void* g_static_workspace_addr[kMaxDevices] = {};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -441,6 +446,56 @@ int b200attn_prefill(void* out, int64_t out_row_stride, const void* q, int64_t q
   if (head_size == 128) return launch_prefill<128, 32>(tq, tk, tv, p, total_tiles, s);
   if (block_size == 64) return launch_prefill<64, 64>(tq, tk, tv, p, total_tiles, s);
   return launch_prefill<64, 32>(tq, tk, tv, p, total_tiles, s);
+}
+
+int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* q,
+                                 int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                                 const int32_t* page_table, int64_t page_table_stride,
+                                 int page_table_width, const int32_t* cur_pos, int num_users,
+                                 int num_q_heads, int num_kv_heads, int head_size, int block_size,
+                                 int64_t num_blocks, float scale, int max_context_len,
+                                 int num_splits, void* stream) {
+  if (num_users < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_splits < 0)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  if (head_size != 64 && head_size != 128) return B200ATTN_ERR_UNSUPPORTED;
+  if (page_table_width <= 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (num_splits > 0) {
+    if (b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits) >
+        B200ATTN_STATIC_WORKSPACE_BYTES)
+      return B200ATTN_ERR_TOO_LARGE;
+  } else {
+    int ctx = max_context_len > 0 ? max_context_len : page_table_width * block_size;
+    num_splits = b200attn_decode_auto_splits(num_users, num_kv_heads, block_size, ctx);
+    while (num_splits > 1 &&
+           b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits) >
+               B200ATTN_STATIC_WORKSPACE_BYTES)
+      --num_splits;
+  }
+  // Per-device set-up, once, with that device current: the device address of the array.
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return B200ATTN_ERR_NO_DEVICE;
+  }
+  void* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_static_workspace_addr[dev]) {
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_static_workspace);
+      if (e != cudaSuccess || !p) {
+        cudaGetLastError();
+        return e != cudaSuccess ? static_cast<int>(e) : B200ATTN_ERR_NO_DEVICE;
+      }
+      g_static_workspace_addr[dev] = p;
+    }
+    ws = g_static_workspace_addr[dev];
+  }
+  return b200attn_paged_decode(out, out_row_stride, q, q_row_stride, k_cache, v_cache,
+                               page_table, page_table_stride, page_table_width, cur_pos,
+                               num_users, num_q_heads, num_kv_heads, head_size, block_size,
+                               num_blocks, scale, max_context_len, num_splits, ws,
+                               B200ATTN_STATIC_WORKSPACE_BYTES, stream);
 }
 
 int b200attn_read_error_word(int32_t* out_host, void* stream) {
