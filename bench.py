@@ -50,6 +50,10 @@ WORKLOADS = {
                desc="c3_decode_rows_llama8b_B64_L1024-8192"),
     "c1": dict(nq=32, nkv=8, hd=64, bs=32, users=8, ctx_lo=128, ctx_hi=1024,
                desc="c1_decode_llama1b_B8_L128-1024"),
+    # config-4 geometry at a quarter of the context and a quarter of the batch: the case
+    # profiler captures run on (268 MB of KV: larger than L2, small enough to replay)
+    "c4s": dict(nq=64, nkv=8, hd=128, bs=64, users=8, ctx_lo=8192, ctx_hi=8192,
+                desc="c4_small_decode_llama70b_B8_L8192"),
 }
 
 
@@ -82,7 +86,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu_index)],
+                 "-lms", "20", "-i", str(self.gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -433,6 +437,8 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "prefill"],
+                    help="prefill: run only the config-2 prefill part (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     wl = WORKLOADS[args.workload]
@@ -449,6 +455,15 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     peaks = load_peaks()
+
+    if args.only == "prefill":
+        pf = run_prefill_bench(args, rank, world, device, peaks)
+        if rank == 0:
+            print(json.dumps({"only": "prefill", "prefill": pf}))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     r = run_decode_bench(args, wl, rank, world, device)
     prefill = None if args.no_prefill else run_prefill_bench(args, rank, world, device, peaks)
