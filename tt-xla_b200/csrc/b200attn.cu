@@ -405,7 +405,7 @@ int b200attn_prefill(void* out, int64_t out_row_stride, const void* q, int64_t q
   for (int s = 0; s < num_seqs; ++s) {
     const int len = cu_q_host[s + 1] - cu_q_host[s];
     if (len < 0) return B200ATTN_ERR_BAD_ARGUMENT;
-    total_tiles += (len + kPfM - 1) / kPfM;
+    total_tiles += (len + kPfRowsPerCta - 1) / kPfRowsPerCta;
   }
   if (cu_q_host[num_seqs] - cu_q_host[0] > total_q) return B200ATTN_ERR_BAD_ARGUMENT;
   if (total_tiles == 0) return B200ATTN_OK;

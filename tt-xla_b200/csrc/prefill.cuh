@@ -1,28 +1,33 @@
 // Causal varlen / chunked prefill attention on tcgen05 tensor cores.
 //
-// One CTA = 128 query rows of one sequence x one query head.  KV is consumed in tiles of
-// 128 keys.  Six warps:
-//   warp 0      TMA producer: Q once, then K_j, V_j, K_j+1, ... into a 4-slot ring of
-//               [2 x 128 rows x 128 B] swizzled sub-tiles (paged source: one box per page;
-//               fresh source: one box per 64-wide column group).
-//   warp 1      allocates tensor memory and issues tcgen05.mma from one thread:
-//               S_j = Q K_j^T (two S buffers, so S_j+1 is computed while S_j is in softmax)
-//               and O += P_j V_j (V as an MN-major B operand straight from the paged layout).
-//   warps 2-5   one thread per query row: tcgen05.ld the row of S, scale + causal mask,
-//               running max with a lazy rescale threshold, exp2, row sum, P as bf16 into a
-//               swizzled shared-memory tile (the A operand of the PV MMA); rescales its O
-//               row in tensor memory when the running max moved; at the end normalises O by
-//               1/l and stores bf16.
+// One CTA = 2 x 128 query rows (tiles A and B) of one sequence x one query head.  KV is
+// consumed in tiles of 128 keys, shared by both query tiles.  Ten warps:
+//   warp 0      TMA producer: Q_A and Q_B once, then K_0, V_0, K_1, V_1, ... into a ring of
+//               swizzled [128 rows x 128 B] sub-tiles (paged source: one box per page; fresh
+//               source: one box per 64-wide column group).
+//   warp 1      allocates tensor memory (S_A, S_B, O_A, O_B = 512 columns) and issues
+//               tcgen05.mma from one thread in the order
+//                   PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...
+//               so that the tensor pipe works for one query tile while the other tile's
+//               softmax runs.  S = Q K^T has both operands K-major; O += P V takes V as an
+//               MN-major B operand straight from the paged [key][d] layout.
+//   warps 2-5   softmax warpgroup of tile A, warps 6-9 of tile B; one thread per query row:
+//               tcgen05.ld the row of S, causal mask on diagonal tiles, running max with a
+//               lazy rescale threshold, ex2 via packed fp32 FMA, row sum, P as bf16 into a
+//               swizzled shared-memory tile (the A operand of the PV MMA); rescales its O row
+//               in tensor memory when the running max moved; at the end normalises O by 1/l
+//               and stores bf16.
 // Every mbarrier wait is bounded; tensor memory is always freed before exit.
 #pragma once
 #include "ptx.cuh"
 
 namespace b200attn {
 
-constexpr int kPfM = 128;        // query rows per CTA
-constexpr int kPfN = 128;        // keys per tile
-constexpr int kPfThreads = 192;
-constexpr int kPfSlots = 4;      // ring slots (each holds one K or one V tile)
+constexpr int kPfM = 128;        // query rows per tile
+constexpr int kPfQTiles = 2;     // query tiles per CTA
+constexpr int kPfRowsPerCta = kPfM * kPfQTiles;
+constexpr int kPfN = 128;        // keys per KV tile
+constexpr int kPfThreads = 320;
 constexpr float kPfRescaleThreshold = 8.f;  // log2 units
 
 struct PrefillParams {
@@ -47,14 +52,16 @@ template <int HD>
 struct PrefillSmem {
   static constexpr int kSub = HD / 64;
   static constexpr int kSubBytes = 128 * 128;             // 128 rows x 128 B
-  static constexpr int kTileBytes = kSub * kSubBytes;     // Q, K or V tile
+  static constexpr int kTileBytes = kSub * kSubBytes;     // one Q, K or V tile
   static constexpr int kPBytes = 2 * kSubBytes;           // P: 128 rows x 128 keys bf16
+  static constexpr int kSlots = (HD == 128) ? 3 : 6;      // ring slots (one K or V tile each)
   static constexpr int kQOff = 0;
-  static constexpr int kPOff = kTileBytes;
-  static constexpr int kRingOff = kPOff + kPBytes;
-  static constexpr int kBarOff = kRingOff + kPfSlots * kTileBytes;
-  static constexpr int kNumBars = 1 + 2 * kPfSlots + 2 + 2 + 2;
+  static constexpr int kPOff = kPfQTiles * kTileBytes;
+  static constexpr int kRingOff = kPOff + kPfQTiles * kPBytes;
+  static constexpr int kBarOff = kRingOff + kSlots * kTileBytes;
+  static constexpr int kNumBars = 1 + 2 * kSlots + 3 * kPfQTiles;
   static constexpr int kTotalBytes = kBarOff + kNumBars * 8 + 16 + 1024;
+  static_assert(kTotalBytes <= 232448, "shared memory budget");
 };
 
 template <int HD, int BS>
@@ -64,6 +71,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                        const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
   using L = PrefillSmem<HD>;
   constexpr int kSub = L::kSub;
+  constexpr int kSlots = L::kSlots;
   constexpr int kPagesPerTile = kPfN / BS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -73,12 +81,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint8_t* ring = smem + L::kRingOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* q_full = bars;
-  uint64_t* full = bars + 1;                 // [kPfSlots]
-  uint64_t* empty = full + kPfSlots;         // [kPfSlots]
-  uint64_t* s_full = empty + kPfSlots;       // [2]
-  uint64_t* s_empty = s_full + 2;            // [2]
-  uint64_t* p_full = s_empty + 2;            // [1]
-  uint64_t* pv_done = p_full + 1;            // [1]
+  uint64_t* full = bars + 1;                 // [kSlots]
+  uint64_t* empty = full + kSlots;           // [kSlots]
+  uint64_t* s_full = empty + kSlots;         // [2]  S of tile A / B ready (MMA -> softmax)
+  uint64_t* p_full = s_full + kPfQTiles;     // [2]  P of tile A / B written (softmax -> MMA)
+  uint64_t* pv_done = p_full + kPfQTiles;    // [2]  PV of tile A / B retired (MMA -> softmax)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -88,17 +95,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   // A CTA of this launch already gave up on a wait: do not repeat the timeout per CTA.
   if (*reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout) return;
 
-  // ---- which (sequence, query tile) is this CTA?  Heavy (late) tiles are scheduled first.
+  // ---- which (sequence, 256-row query block) is this CTA?  Heavy (late) blocks go first.
   int tile_linear = gridDim.x - 1 - blockIdx.x;
   int seq = -1, q0 = 0, seq_q_begin = 0, seq_len_q = 0;
   {
     int acc = 0;
     for (int s = 0; s < p.num_seqs; ++s) {
       const int b = p.cu_q[s], e = p.cu_q[s + 1];
-      const int nt = (e - b + kPfM - 1) / kPfM;
+      const int nt = (e - b + kPfRowsPerCta - 1) / kPfRowsPerCta;
       if (tile_linear < acc + nt) {
         seq = s;
-        q0 = (tile_linear - acc) * kPfM;
+        q0 = (tile_linear - acc) * kPfRowsPerCta;
         seq_q_begin = b;
         seq_len_q = e - b;
         break;
@@ -110,23 +117,27 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int head = blockIdx.y;
   const int kvh = head / p.group;
   const int start = p.q_start ? p.q_start[seq] : 0;
-  const int rows_valid = min(kPfM, seq_len_q - q0);
-  const int first_pos = start + q0;                   // absolute position of row 0
-  const int last_pos = first_pos + rows_valid - 1;    // last valid row
-  const int n_tiles = last_pos / kPfN + 1;            // key tiles 0 .. n_tiles-1
+  // Per query tile: valid rows, first absolute position, number of KV tiles it attends to.
+  int rows_valid[kPfQTiles], first_pos[kPfQTiles], n_tiles[kPfQTiles];
+#pragma unroll
+  for (int w = 0; w < kPfQTiles; ++w) {
+    rows_valid[w] = max(0, min(kPfM, seq_len_q - q0 - w * kPfM));
+    first_pos[w] = start + q0 + w * kPfM;
+    n_tiles[w] = rows_valid[w] > 0 ? (first_pos[w] + rows_valid[w] - 1) / kPfN + 1 : 0;
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);   // tile A never needs more KV tiles than B
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < kPfSlots; ++i) {
+    for (int i = 0; i < kSlots; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kPfQTiles; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&pv_done[i], 1);
     }
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -138,8 +149,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s0 = tmem_base;          // S buffers: columns [0,128) and [128,256)
-  const uint32_t tmem_o = tmem_base + 256;     // O: columns [256, 256+HD)
+  // columns: S_A [0,128)  S_B [128,256)  O_A [256,256+HD)  O_B [384,384+HD)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -148,20 +158,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       const uint64_t pol_q = l2_policy_evict_first();
-      mbar_arrive_expect_tx(q_full, L::kTileBytes);
+      mbar_arrive_expect_tx(q_full, kPfQTiles * L::kTileBytes);
 #pragma unroll
-      for (int s = 0; s < kSub; ++s)
-        tma_load_2d(q_smem + s * L::kSubBytes, &tm_q, q_full, head * HD + s * 64,
-                    seq_q_begin + q0, pol_q);
+      for (int w = 0; w < kPfQTiles; ++w)
+#pragma unroll
+        for (int s = 0; s < kSub; ++s)
+          tma_load_2d(q_smem + w * L::kTileBytes + s * L::kSubBytes, &tm_q, q_full,
+                      head * HD + s * 64, seq_q_begin + q0 + w * kPfM, pol_q);
     }
     const uint64_t pol_kv = l2_policy_evict_last();
     const int32_t* pt = p.page_table + static_cast<int64_t>(seq) * p.page_table_stride;
-    const int n_pages = (last_pos + BS) / BS;   // pages holding keys 0 .. last_pos
-    for (int i = 0; i < 2 * n_tiles; ++i) {
+    const int last_pos = start + min(seq_len_q, q0 + kPfRowsPerCta) - 1;
+    const int n_pages = last_pos / BS + 1;      // pages holding keys 0 .. last_pos
+    for (int i = 0; i < 2 * n_max; ++i) {
       const int j = i >> 1;
       const bool is_v = i & 1;
-      const int slot = i % kPfSlots;
-      mbar_wait(&empty[slot], ((i / kPfSlots) & 1) ^ 1, abort_flag, p.err_word);
+      const int slot = i % kSlots;
+      mbar_wait(&empty[slot], ((i / kSlots) & 1) ^ 1, abort_flag, p.err_word);
       uint8_t* dst = ring + slot * L::kTileBytes;
       const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
       if (lane == 0) mbar_arrive_expect_tx(&full[slot], L::kTileBytes);
@@ -199,145 +212,203 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfM, kPfN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true);
-      const uint32_t q_addr = smem_u32(q_smem);
-      const uint32_t p_addr = smem_u32(p_smem);
-      auto issue_qk = [&](int j) {
-        const int i = 2 * j, slot = i % kPfSlots;
-        mbar_wait(&full[slot], (i / kPfSlots) & 1, abort_flag, p.err_word);
-        if (j >= 2) mbar_wait(&s_empty[j & 1], ((j - 2) >> 1) & 1, abort_flag, p.err_word);
+      auto wait_item = [&](int i) {
+        mbar_wait(&full[i % kSlots], (i / kSlots) & 1, abort_flag, p.err_word);
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(ring + slot * L::kTileBytes);
-        const uint32_t d = tmem_s0 + (j & 1) * kPfN;
+      };
+      auto release_item = [&](int i) { umma_commit(&empty[i % kSlots]); };
+      auto issue_qk = [&](int w, int j) {   // S_w = Q_w K_j^T
+        const uint32_t q_addr = smem_u32(q_smem + w * L::kTileBytes);
+        const uint32_t k_addr = smem_u32(ring + ((2 * j) % kSlots) * L::kTileBytes);
+        const uint32_t d = tmem_base + w * kPfN;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * L::kSubBytes + (kk & 3) * 32;
           umma_ss(d, umma_smem_desc_sw128(q_addr + off, 16, 1024),
                   umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0);
         }
-        umma_commit(&s_full[j & 1]);
-        umma_commit(&empty[slot]);
+        umma_commit(&s_full[w]);
       };
-      mbar_wait(q_full, 0, abort_flag, p.err_word);
-      issue_qk(0);
-      for (int j = 0; j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) issue_qk(j + 1);
-        const int i = 2 * j + 1, slot = i % kPfSlots;
-        mbar_wait(&full[slot], (i / kPfSlots) & 1, abort_flag, p.err_word);
-        mbar_wait(p_full, j & 1, abort_flag, p.err_word);
+      auto issue_pv = [&](int w, int j) {   // O_w += P_w V_j
+        mbar_wait(&p_full[w], j & 1, abort_flag, p.err_word);
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(ring + slot * L::kTileBytes);
+        const uint32_t p_addr = smem_u32(p_smem + w * L::kPBytes);
+        const uint32_t v_addr = smem_u32(ring + ((2 * j + 1) % kSlots) * L::kTileBytes);
+        const uint32_t d = tmem_base + 256 + w * 128;
 #pragma unroll
         for (int kk = 0; kk < kPfN / 16; ++kk) {
           const uint32_t a_off = (kk >> 2) * L::kSubBytes + (kk & 3) * 32;
-          umma_ss(tmem_o, umma_smem_desc_sw128(p_addr + a_off, 16, 1024),
+          umma_ss(d, umma_smem_desc_sw128(p_addr + a_off, 16, 1024),
                   umma_smem_desc_sw128(v_addr + kk * 2048, L::kSubBytes, 1024), idesc_pv,
                   (j > 0) || (kk > 0));
         }
-        umma_commit(pv_done);
-        umma_commit(&empty[slot]);
+        umma_commit(&pv_done[w]);
+      };
+      mbar_wait(q_full, 0, abort_flag, p.err_word);
+      wait_item(0);
+#pragma unroll
+      for (int w = 0; w < kPfQTiles; ++w)
+        if (n_tiles[w] > 0) issue_qk(w, 0);
+      release_item(0);
+      for (int j = 0; j < n_max; ++j) {
+        wait_item(2 * j + 1);                       // V_j
+        const bool has_next = j + 1 < n_max;
+        bool next_k_ready = false;
+#pragma unroll
+        for (int w = 0; w < kPfQTiles; ++w) {
+          if (j < n_tiles[w]) {
+            issue_pv(w, j);
+            if (j + 1 < n_tiles[w]) {
+              if (!next_k_ready) {
+                wait_item(2 * j + 2);               // K_{j+1}
+                next_k_ready = true;
+              }
+              issue_qk(w, j + 1);
+            }
+          }
+        }
+        release_item(2 * j + 1);
+        if (has_next) release_item(2 * j + 2);
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
+    const int w = (warp - 2) >> 2;                       // 0 = tile A, 1 = tile B
     const int row = (warp & 3) * 32 + lane;              // tensor-memory lane == query row
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int q_pos = first_pos + row;
+    const uint32_t s_addr = tmem_base + w * kPfN + lane_addr;
+    const uint32_t o_addr = tmem_base + 256 + w * 128 + lane_addr;
+    const int q_pos = first_pos[w] + row;
+    const int my_tiles = n_tiles[w];
+    const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
     float m_run = -INFINITY, l_run = 0.f;
-    for (int j = 0; j < n_tiles; ++j) {
-      mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.err_word);
+    for (int j = 0; j < my_tiles; ++j) {
+      mbar_wait(&s_full[w], j & 1, abort_flag, p.err_word);
       tc_fence_after_sync();
       uint32_t sreg[4][32];
-      const uint32_t s_addr = tmem_s0 + (j & 1) * kPfN + lane_addr;
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
       tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(&s_empty[j & 1]);
 
       const int key0 = j * kPfN;
-      const bool need_mask = key0 + kPfN - 1 > first_pos;
-      float mx = -INFINITY;
+      if (key0 + kPfN - 1 > first_pos[w]) {     // tile crosses the diagonal for some row
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          float v = __uint_as_float(sreg[c][k]) * p.scale_log2;
-          if (need_mask && (key0 + c * 32 + k > q_pos)) v = -INFINITY;
-          sreg[c][k] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+          for (int k = 0; k < 32; ++k)
+            if (key0 + c * 32 + k > q_pos) sreg[c][k] = 0xff800000u;   // -inf
+      }
+      // row max of the raw scores (scale > 0), four independent chains
+      float mx[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        mx[c] = max3(__uint_as_float(sreg[c][0]), __uint_as_float(sreg[c][1]),
+                     __uint_as_float(sreg[c][2]));
+#pragma unroll
+        for (int k = 3; k + 1 < 32; k += 2)
+          mx[c] = max3(mx[c], __uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1]));
+        mx[c] = fmaxf(mx[c], __uint_as_float(sreg[c][31]));
+      }
+      const float mx_s = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
       float m_new = m_run;
-      if (mx - m_run > kPfRescaleThreshold) m_new = mx;   // also taken when m_run = -inf
+      if (mx_s - m_run > kPfRescaleThreshold) m_new = mx_s;   // also taken when m_run = -inf
       const float corr = fast_exp2(m_run - m_new);
       const bool rescale = (m_new != m_run) && (j > 0);
       m_run = m_new;
-      float sum = 0.f;
-      uint32_t preg[64];
+      if (j > 0) {
+        // PV_{j-1} must have retired before P is overwritten or O is rescaled.  It was issued
+        // before QK_j, whose completion s_full just signalled, so this wait does not block.
+        mbar_wait(&pv_done[w], (j - 1) & 1, abort_flag, p.err_word);
+        tc_fence_after_sync();
+      }
+      // p = 2^(s*scale - m): packed FMA, then ex2; two packed running sums.  Each 32-key chunk
+      // goes straight to the swizzled K-major P tile (16-byte piece jj covers keys jj*8..+7).
+      const uint64_t negm2 = pack_f32x2(-m_new, -m_new);
+      const uint32_t p_row = smem_u32(p_smem + w * L::kPBytes) + row * 128;
+      uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 4; ++c) {
+        uint32_t preg[16];
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
-          const float e0 = fast_exp2(__uint_as_float(sreg[c][k]) - m_new);
-          const float e1 = fast_exp2(__uint_as_float(sreg[c][k + 1]) - m_new);
-          sum += e0 + e1;
-          preg[(c * 32 + k) >> 1] = pack_bf16x2(e0, e1);
+          const uint64_t x2 = fma_f32x2(
+              pack_f32x2(__uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1])), scale2,
+              negm2);
+          float x0, x1;
+          unpack_f32x2(x2, x0, x1);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          sum2[(k >> 1) & 1] = add_f32x2(sum2[(k >> 1) & 1], pack_f32x2(e0, e1));
+          preg[k >> 1] = pack_bf16x2(e0, e1);
         }
-      l_run = l_run * corr + sum;
-
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int jj = c * 4 + q4;
+          const uint32_t a = p_row + (jj >> 3) * L::kSubBytes + (((jj & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(preg[q4 * 4]),
+                       "r"(preg[q4 * 4 + 1]), "r"(preg[q4 * 4 + 2]), "r"(preg[q4 * 4 + 3])
+                       : "memory");
+        }
+      }
+      {
+        float a0, a1, b0, b1;
+        unpack_f32x2(sum2[0], a0, a1);
+        unpack_f32x2(sum2[1], b0, b1);
+        l_run = l_run * corr + ((a0 + a1) + (b0 + b1));
+      }
+      // O row rescale (rare: only when the running max moved by more than the threshold).
       if (j > 0) {
-        // PV_{j-1} must have retired before P is overwritten or O is rescaled.
-        mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.err_word);
-        tc_fence_after_sync();
         if (__any_sync(0xffffffffu, rescale)) {
           const float f = rescale ? corr : 1.f;
+          const uint64_t f2 = pack_f32x2(f, f);
 #pragma unroll
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t oreg[32];
-            tmem_ld_32x32(tmem_o + lane_addr + c * 32, oreg);
+            tmem_ld_32x32(o_addr + c * 32, oreg);
             tmem_wait_ld();
 #pragma unroll
-            for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * f);
-            tmem_st_32x32(tmem_o + lane_addr + c * 32, oreg);
+            for (int k = 0; k < 32; k += 2) {
+              float y0, y1;
+              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(oreg[k]),
+                                                __uint_as_float(oreg[k + 1])), f2), y0, y1);
+              oreg[k] = __float_as_uint(y0);
+              oreg[k + 1] = __float_as_uint(y1);
+            }
+            tmem_st_32x32(o_addr + c * 32, oreg);
           }
           tmem_wait_st();
         }
       }
-      // P row -> swizzled K-major tile: 16-byte chunk jj covers keys jj*8 .. jj*8+7.
-      const uint32_t p_row = smem_u32(p_smem) + row * 128;
-#pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
-        const uint32_t a = p_row + (jj >> 3) * L::kSubBytes + (((jj & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(preg[jj * 4]),
-                     "r"(preg[jj * 4 + 1]), "r"(preg[jj * 4 + 2]), "r"(preg[jj * 4 + 3])
-                     : "memory");
-      }
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[w]);
     }
     // ---- epilogue: O / l -> bf16 rows
-    mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag, p.err_word);
-    tc_fence_after_sync();
-    const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* orow = p.out + static_cast<int64_t>(seq_q_begin + q0 + row) * p.out_row_stride +
-                          static_cast<int64_t>(head) * HD;
+    if (my_tiles > 0) {
+      mbar_wait(&pv_done[w], (my_tiles - 1) & 1, abort_flag, p.err_word);
+      tc_fence_after_sync();
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow =
+          p.out + static_cast<int64_t>(seq_q_begin + q0 + w * kPfM + row) * p.out_row_stride +
+          static_cast<int64_t>(head) * HD;
 #pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      uint32_t oreg[32];
-      tmem_ld_32x32(tmem_o + lane_addr + c * 32, oreg);
-      tmem_wait_ld();
-      if (row < rows_valid) {
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t oreg[32];
+        tmem_ld_32x32(o_addr + c * 32, oreg);
+        tmem_wait_ld();
+        if (row < rows_valid[w]) {
 #pragma unroll
-        for (int k = 0; k < 32; k += 8) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(oreg[k]) * inv_l, __uint_as_float(oreg[k + 1]) * inv_l);
-          v.y = pack_bf16x2(__uint_as_float(oreg[k + 2]) * inv_l,
-                            __uint_as_float(oreg[k + 3]) * inv_l);
-          v.z = pack_bf16x2(__uint_as_float(oreg[k + 4]) * inv_l,
-                            __uint_as_float(oreg[k + 5]) * inv_l);
-          v.w = pack_bf16x2(__uint_as_float(oreg[k + 6]) * inv_l,
-                            __uint_as_float(oreg[k + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(orow + c * 32 + k) = v;
+          for (int k = 0; k < 32; k += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(oreg[k]) * inv_l,
+                              __uint_as_float(oreg[k + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(oreg[k + 2]) * inv_l,
+                              __uint_as_float(oreg[k + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(oreg[k + 4]) * inv_l,
+                              __uint_as_float(oreg[k + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(oreg[k + 6]) * inv_l,
+                              __uint_as_float(oreg[k + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + k) = v;
+          }
         }
       }
     }
