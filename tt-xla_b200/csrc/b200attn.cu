@@ -172,13 +172,14 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
 
 template <int HD, int BS>
 static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                          const PrefillParams& p, int total_tiles, cudaStream_t s) {
+                          const PrefillParams& p, int sm_count, cudaStream_t s) {
   using L = PrefillSmem<HD>;
   auto kern = prefill_tcgen05_kernel<HD, BS>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid(total_tiles, p.num_q_heads);
+  // persistent: one CTA per SM (the kernel holds all of an SM's shared and tensor memory)
+  dim3 grid(static_cast<unsigned>(p.total_items < sm_count ? p.total_items : sm_count));
   kern<<<grid, kPfThreads, L::kTotalBytes, s>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -405,11 +406,11 @@ int b200attn_prefill(void* out, int64_t out_row_stride, const void* q, int64_t q
   for (int s = 0; s < num_seqs; ++s) {
     const int len = cu_q_host[s + 1] - cu_q_host[s];
     if (len < 0) return B200ATTN_ERR_BAD_ARGUMENT;
-    total_tiles += (len + kPfRowsPerCta - 1) / kPfRowsPerCta;
+    total_tiles += (len + kPfRowsPerItem - 1) / kPfRowsPerItem;
   }
   if (cu_q_host[num_seqs] - cu_q_host[0] > total_q) return B200ATTN_ERR_BAD_ARGUMENT;
   if (total_tiles == 0) return B200ATTN_OK;
-  if (num_q_heads > 65535) return B200ATTN_ERR_TOO_LARGE;
+  if (static_cast<int64_t>(total_tiles) * num_q_heads > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
 
   CUtensorMap tq, tk, tv;
   if (int rc = make_map(&tq, q, total_q, static_cast<uint64_t>(num_q_heads) * head_size,
@@ -438,14 +439,15 @@ int b200attn_prefill(void* out, int64_t out_row_stride, const void* q, int64_t q
   p.num_kv_heads = num_kv_heads;
   p.group = num_q_heads / num_kv_heads;
   p.kv_is_paged = kv_is_paged ? 1 : 0;
+  p.total_items = total_tiles * num_q_heads;
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err_word = dev->err_word;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (head_size == 128 && block_size == 64) return launch_prefill<128, 64>(tq, tk, tv, p, total_tiles, s);
-  if (head_size == 128) return launch_prefill<128, 32>(tq, tk, tv, p, total_tiles, s);
-  if (block_size == 64) return launch_prefill<64, 64>(tq, tk, tv, p, total_tiles, s);
-  return launch_prefill<64, 32>(tq, tk, tv, p, total_tiles, s);
+  if (head_size == 128 && block_size == 64) return launch_prefill<128, 64>(tq, tk, tv, p, dev->sm_count, s);
+  if (head_size == 128) return launch_prefill<128, 32>(tq, tk, tv, p, dev->sm_count, s);
+  if (block_size == 64) return launch_prefill<64, 64>(tq, tk, tv, p, dev->sm_count, s);
+  return launch_prefill<64, 32>(tq, tk, tv, p, dev->sm_count, s);
 }
 
 int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* q,
@@ -497,6 +499,16 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* 
                                num_blocks, scale, max_context_len, num_splits, ws,
                                B200ATTN_STATIC_WORKSPACE_BYTES, stream);
 }
+
+#ifdef B200ATTN_PREFILL_TRACE
+// Debug build only: copies the prefill trace stamps to the host.
+int b200attn_debug_read_prefill_trace(long long* out_host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out_host, g_pf_trace, sizeof(long long) * n));
+}
+int b200attn_debug_read_prefill_cta_trace(long long* out_host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out_host, g_pf_cta, sizeof(long long) * n));
+}
+#endif
 
 int b200attn_read_error_word(int32_t* out_host, void* stream) {
   if (!out_host) return B200ATTN_ERR_NULL_POINTER;

@@ -1,22 +1,27 @@
 // Causal varlen / chunked prefill attention on tcgen05 tensor cores.
 //
-// One CTA = 2 x 128 query rows (tiles A and B) of one sequence x one query head.  KV is
-// consumed in tiles of 128 keys, shared by both query tiles.  Ten warps:
-//   warp 0      TMA producer: Q_A and Q_B once, then K_0, V_0, K_1, V_1, ... into a ring of
-//               swizzled [128 rows x 128 B] sub-tiles (paged source: one box per page; fresh
-//               source: one box per 64-wide column group).
-//   warp 1      allocates tensor memory (S_A, S_B, O_A, O_B = 512 columns) and issues
-//               tcgen05.mma from one thread in the order
+// Persistent kernel: one CTA per SM walks a list of work items; an item is 2 x 128 query
+// rows (tiles A and B) of one sequence x one query head.  KV is consumed in tiles of 128
+// keys, shared by both query tiles.  Ten warps:
+//   warp 0      TMA producer: per item Q_A and Q_B, then K_0, V_0, K_1, V_1, ... into a ring
+//               of swizzled [128 rows x 128 B] sub-tiles (paged source: one box per page;
+//               fresh source: one box per 64-wide column group).  It runs ahead of the other
+//               warps, so the loads of the next item overlap the tail of the current one.
+//   warp 1      allocates tensor memory once (S_A, S_B, O_A, O_B = 512 columns) and issues
+//               tcgen05.mma from one lane in the order
 //                   PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...
 //               so that the tensor pipe works for one query tile while the other tile's
-//               softmax runs.  S = Q K^T has both operands K-major; O += P V takes V as an
-//               MN-major B operand straight from the paged [key][d] layout.
+//               softmax runs; at an item boundary it goes straight on to QK(0) of the next
+//               item while the softmax warps are still in their epilogue.
 //   warps 2-5   softmax warpgroup of tile A, warps 6-9 of tile B; one thread per query row:
 //               tcgen05.ld the row of S, causal mask on diagonal tiles, running max with a
-//               lazy rescale threshold, ex2 via packed fp32 FMA, row sum, P as bf16 into a
-//               swizzled shared-memory tile (the A operand of the PV MMA); rescales its O row
-//               in tensor memory when the running max moved; at the end normalises O by 1/l
-//               and stores bf16.
+//               lazy rescale threshold, ex2 via packed fp32 FMA, row sum, P as packed bf16 back
+//               into tensor memory over the first 64 columns of its S buffer (the PV MMA takes
+//               its A operand from tensor memory); rescales its O row in tensor memory when the
+//               running max moved; per item it normalises O by 1/l and stores bf16.
+// Items are ordered heaviest first (by the index of the 256-row block inside its sequence,
+// highest first, heads of one block adjacent) and dealt to the CTAs in rounds of alternating
+// direction (0..G-1, G-1..0, ...), which evens out the per-CTA sums of a sorted list.
 // Every mbarrier wait is bounded; tensor memory is always freed before exit.
 #pragma once
 #include "ptx.cuh"
@@ -24,11 +29,13 @@
 namespace b200attn {
 
 constexpr int kPfM = 128;        // query rows per tile
-constexpr int kPfQTiles = 2;     // query tiles per CTA
-constexpr int kPfRowsPerCta = kPfM * kPfQTiles;
+constexpr int kPfQTiles = 2;     // query tiles per item
+constexpr int kPfRowsPerItem = kPfM * kPfQTiles;
 constexpr int kPfN = 128;        // keys per KV tile
 constexpr int kPfThreads = 320;
 constexpr float kPfRescaleThreshold = 8.f;  // log2 units
+constexpr int kPfSeqCache = 2048;           // sequences whose cu_q is cached in shared memory
+constexpr int kPfLevelOrderMaxSeqs = 64;    // above this, items keep plain sequence order
 
 struct PrefillParams {
   __nv_bfloat16* out;
@@ -43,6 +50,7 @@ struct PrefillParams {
   int num_kv_heads;
   int group;
   int kv_is_paged;
+  int total_items;     // (256-row blocks over all sequences) x num_q_heads
   int64_t num_blocks;
   float scale_log2;
   int* err_word;
@@ -53,16 +61,91 @@ struct PrefillSmem {
   static constexpr int kSub = HD / 64;
   static constexpr int kSubBytes = 128 * 128;             // 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;     // one Q, K or V tile
-  static constexpr int kPBytes = 2 * kSubBytes;           // P: 128 rows x 128 keys bf16
-  static constexpr int kSlots = (HD == 128) ? 3 : 6;      // ring slots (one K or V tile each)
+  static constexpr int kSlots = (HD == 128) ? 4 : 8;      // ring slots (one K or V tile each)
   static constexpr int kQOff = 0;
-  static constexpr int kPOff = kPfQTiles * kTileBytes;
-  static constexpr int kRingOff = kPOff + kPfQTiles * kPBytes;
-  static constexpr int kBarOff = kRingOff + kSlots * kTileBytes;
-  static constexpr int kNumBars = 1 + 2 * kSlots + 3 * kPfQTiles;
+  static constexpr int kRingOff = kPfQTiles * kTileBytes;
+  static constexpr int kSeqOff = kRingOff + kSlots * kTileBytes;
+  static constexpr int kBarOff = kSeqOff + (kPfSeqCache + 2) * 4;
+  static constexpr int kNumBars = 2 + 2 * kSlots + 4 * kPfQTiles;
   static constexpr int kTotalBytes = kBarOff + kNumBars * 8 + 16 + 1024;
+  static_assert(kBarOff % 8 == 0, "barrier alignment");
   static_assert(kTotalBytes <= 232448, "shared memory budget");
 };
+
+// What every role needs to know about one work item.
+struct PrefillItem {
+  int seq, head, q0, seq_q_begin, seq_len_q, start;
+  int rows_valid[kPfQTiles], first_pos[kPfQTiles], n_tiles[kPfQTiles];
+  int n_max;
+};
+
+// Item index -> (sequence, 256-row block, head).  `cu` is cu_q (shared-memory copy when the
+// batch fits the cache).  Heaviest first: blocks ranked by their index inside their sequence,
+// highest first across sequences; the heads of one block are adjacent.
+__device__ __forceinline__ bool prefill_decode_item(const PrefillParams& p, const int32_t* cu,
+                                                    int item, PrefillItem& it) {
+  it.head = item % p.num_q_heads;
+  const int t = item / p.num_q_heads;
+  auto nblk = [&](int s) { return (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem; };
+  int seq = -1, blk = 0;
+  if (p.num_seqs <= kPfLevelOrderMaxSeqs) {
+    int max_n = 0;
+    for (int s = 0; s < p.num_seqs; ++s) max_n = max(max_n, nblk(s));
+    auto at_or_above = [&](int r) {   // number of blocks whose index is >= r; decreasing in r
+      int n = 0;
+      for (int s = 0; s < p.num_seqs; ++s) n += max(0, nblk(s) - r);
+      return n;
+    };
+    if (max_n == 0 || t >= at_or_above(0)) return false;
+    int lo = 0, hi = max_n - 1;       // largest r with at_or_above(r) > t
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (at_or_above(mid) > t) lo = mid; else hi = mid - 1;
+    }
+    int idx = t - at_or_above(lo + 1);
+    for (int s = 0; s < p.num_seqs; ++s) {
+      if (nblk(s) > lo) {
+        if (idx == 0) {
+          seq = s;
+          break;
+        }
+        --idx;
+      }
+    }
+    blk = lo;
+  } else {
+    int acc = 0;
+    for (int s = 0; s < p.num_seqs; ++s) {
+      const int n = nblk(s);
+      if (t < acc + n) {
+        seq = s;
+        blk = n - 1 - (t - acc);      // later blocks of a sequence first
+        break;
+      }
+      acc += n;
+    }
+  }
+  if (seq < 0) return false;
+  it.seq = seq;
+  it.q0 = blk * kPfRowsPerItem;
+  it.seq_q_begin = cu[seq];
+  it.seq_len_q = cu[seq + 1] - cu[seq];
+  it.start = p.q_start ? p.q_start[seq] : 0;
+#pragma unroll
+  for (int w = 0; w < kPfQTiles; ++w) {
+    it.rows_valid[w] = max(0, min(kPfM, it.seq_len_q - it.q0 - w * kPfM));
+    it.first_pos[w] = it.start + it.q0 + w * kPfM;
+    it.n_tiles[w] =
+        it.rows_valid[w] > 0 ? (it.first_pos[w] + it.rows_valid[w] - 1) / kPfN + 1 : 0;
+  }
+  it.n_max = max(it.n_tiles[0], it.n_tiles[1]);   // tile A never needs more KV tiles than B
+  return true;
+}
+
+// Item handled by CTA `cta` of `num_ctas` in round `round` (alternating direction per round).
+__device__ __forceinline__ int prefill_item_of(int round, int cta, int num_ctas) {
+  return round * num_ctas + ((round & 1) ? (num_ctas - 1 - cta) : cta);
+}
 
 template <int HD, int BS>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -77,15 +160,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem + L::kQOff;
-  uint8_t* p_smem = smem + L::kPOff;
   uint8_t* ring = smem + L::kRingOff;
+  int32_t* cu_smem = reinterpret_cast<int32_t*>(smem + L::kSeqOff);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* q_full = bars;
-  uint64_t* full = bars + 1;                 // [kSlots]
+  uint64_t* q_full = bars;                   // Q tiles of the item landed (TMA -> MMA)
+  uint64_t* q_empty = bars + 1;              // last QK of the item retired (MMA -> TMA)
+  uint64_t* full = bars + 2;                 // [kSlots]
   uint64_t* empty = full + kSlots;           // [kSlots]
   uint64_t* s_full = empty + kSlots;         // [2]  S of tile A / B ready (MMA -> softmax)
   uint64_t* p_full = s_full + kPfQTiles;     // [2]  P of tile A / B written (softmax -> MMA)
   uint64_t* pv_done = p_full + kPfQTiles;    // [2]  PV of tile A / B retired (MMA -> softmax)
+  uint64_t* o_empty = pv_done + kPfQTiles;   // [2]  O of tile A / B read out (softmax -> MMA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -95,40 +180,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   // A CTA of this launch already gave up on a wait: do not repeat the timeout per CTA.
   if (*reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout) return;
 
-  // ---- which (sequence, 256-row query block) is this CTA?  Heavy (late) blocks go first.
-  int tile_linear = gridDim.x - 1 - blockIdx.x;
-  int seq = -1, q0 = 0, seq_q_begin = 0, seq_len_q = 0;
-  {
-    int acc = 0;
-    for (int s = 0; s < p.num_seqs; ++s) {
-      const int b = p.cu_q[s], e = p.cu_q[s + 1];
-      const int nt = (e - b + kPfRowsPerCta - 1) / kPfRowsPerCta;
-      if (tile_linear < acc + nt) {
-        seq = s;
-        q0 = (tile_linear - acc) * kPfRowsPerCta;
-        seq_q_begin = b;
-        seq_len_q = e - b;
-        break;
-      }
-      acc += nt;
-    }
-  }
-  if (seq < 0) return;  // uniform for the whole CTA; nothing allocated yet
-  const int head = blockIdx.y;
-  const int kvh = head / p.group;
-  const int start = p.q_start ? p.q_start[seq] : 0;
-  // Per query tile: valid rows, first absolute position, number of KV tiles it attends to.
-  int rows_valid[kPfQTiles], first_pos[kPfQTiles], n_tiles[kPfQTiles];
-#pragma unroll
-  for (int w = 0; w < kPfQTiles; ++w) {
-    rows_valid[w] = max(0, min(kPfM, seq_len_q - q0 - w * kPfM));
-    first_pos[w] = start + q0 + w * kPfM;
-    n_tiles[w] = rows_valid[w] > 0 ? (first_pos[w] + rows_valid[w] - 1) / kPfN + 1 : 0;
-  }
-  const int n_max = max(n_tiles[0], n_tiles[1]);   // tile A never needs more KV tiles than B
+  const bool cu_cached = p.num_seqs <= kPfSeqCache;
+  if (cu_cached)
+    for (int s = threadIdx.x; s <= p.num_seqs; s += blockDim.x) cu_smem[s] = p.cu_q[s];
+  const int32_t* cu = cu_cached ? cu_smem : p.cu_q;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int i = 0; i < kSlots; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
@@ -137,6 +196,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
       mbar_init(&pv_done[i], 1);
+      mbar_init(&o_empty[i], 128);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -157,119 +217,168 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
-      const uint64_t pol_q = l2_policy_evict_first();
-      mbar_arrive_expect_tx(q_full, kPfQTiles * L::kTileBytes);
-#pragma unroll
-      for (int w = 0; w < kPfQTiles; ++w)
-#pragma unroll
-        for (int s = 0; s < kSub; ++s)
-          tma_load_2d(q_smem + w * L::kTileBytes + s * L::kSubBytes, &tm_q, q_full,
-                      head * HD + s * 64, seq_q_begin + q0 + w * kPfM, pol_q);
     }
+    const uint64_t pol_q = l2_policy_evict_first();
     const uint64_t pol_kv = l2_policy_evict_last();
-    const int32_t* pt = p.page_table + static_cast<int64_t>(seq) * p.page_table_stride;
-    const int last_pos = start + min(seq_len_q, q0 + kPfRowsPerCta) - 1;
-    const int n_pages = last_pos / BS + 1;      // pages holding keys 0 .. last_pos
-    for (int i = 0; i < 2 * n_max; ++i) {
-      const int j = i >> 1;
-      const bool is_v = i & 1;
-      const int slot = i % kSlots;
-      mbar_wait(&empty[slot], ((i / kSlots) & 1) ^ 1, abort_flag, p.err_word);
-      uint8_t* dst = ring + slot * L::kTileBytes;
-      const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
-      if (lane == 0) mbar_arrive_expect_tx(&full[slot], L::kTileBytes);
-      if (p.kv_is_paged) {
-        int my_id = 0;
-        if (lane < kPagesPerTile) {
-          int idx = min(j * kPagesPerTile + lane, n_pages - 1);
-          idx = min(idx, p.page_table_width - 1);
-          my_id = pt[idx];
-        }
+    uint32_t ring_i = 0, item_n = 0;
+    for (int round = 0;; ++round) {
+      const int item = prefill_item_of(round, blockIdx.x, gridDim.x);
+      if (round * static_cast<int>(gridDim.x) >= p.total_items) break;
+      if (item >= p.total_items) continue;
+      PrefillItem it;
+      if (!prefill_decode_item(p, cu, item, it)) continue;
+      const int kvh = it.head / p.group;
+      // Q may be overwritten once every QK of the previous item has retired.
+      mbar_wait(q_empty, (item_n & 1) ^ 1, abort_flag, p.err_word);
+      ++item_n;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(q_full, kPfQTiles * L::kTileBytes);
 #pragma unroll
-        for (int pg = 0; pg < kPagesPerTile; ++pg) {
-          int64_t blk = __shfl_sync(0xffffffffu, my_id, pg);
-          if (blk < 0 || blk >= p.num_blocks) {
-            if (lane == 0) atomicExch(p.err_word, kDevBadIndex);
-            blk = 0;
+        for (int w = 0; w < kPfQTiles; ++w)
+#pragma unroll
+          for (int s = 0; s < kSub; ++s)
+            tma_load_2d(q_smem + w * L::kTileBytes + s * L::kSubBytes, &tm_q, q_full,
+                        it.head * HD + s * 64, it.seq_q_begin + it.q0 + w * kPfM, pol_q);
+      }
+      const int32_t* pt = p.page_table + static_cast<int64_t>(it.seq) * p.page_table_stride;
+      const int last_pos = it.start + min(it.seq_len_q, it.q0 + kPfRowsPerItem) - 1;
+      const int n_pages = last_pos / BS + 1;      // pages holding keys 0 .. last_pos
+      for (int i = 0; i < 2 * it.n_max; ++i, ++ring_i) {
+        const int j = i >> 1;
+        const bool is_v = i & 1;
+        const int slot = ring_i % kSlots;
+        mbar_wait(&empty[slot], ((ring_i / kSlots) & 1) ^ 1, abort_flag, p.err_word);
+        uint8_t* dst = ring + slot * L::kTileBytes;
+        const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+        if (lane == 0) mbar_arrive_expect_tx(&full[slot], L::kTileBytes);
+        if (p.kv_is_paged) {
+          int my_id = 0;
+          if (lane < kPagesPerTile) {
+            int idx = min(j * kPagesPerTile + lane, n_pages - 1);
+            idx = min(idx, p.page_table_width - 1);
+            my_id = pt[idx];
           }
-          if (lane == 0) {
-            const int32_t y = static_cast<int32_t>((blk * p.num_kv_heads + kvh) * BS);
 #pragma unroll
-            for (int s = 0; s < kSub; ++s)
-              tma_load_2d(dst + s * L::kSubBytes + pg * BS * 128, tm, &full[slot], s * 64, y,
-                          pol_kv);
+          for (int pg = 0; pg < kPagesPerTile; ++pg) {
+            int64_t blk = __shfl_sync(0xffffffffu, my_id, pg);
+            if (blk < 0 || blk >= p.num_blocks) {
+              if (lane == 0) atomicExch(p.err_word, kDevBadIndex);
+              blk = 0;
+            }
+            if (lane == 0) {
+              const int32_t y = static_cast<int32_t>((blk * p.num_kv_heads + kvh) * BS);
+#pragma unroll
+              for (int s = 0; s < kSub; ++s)
+                tma_load_2d(dst + s * L::kSubBytes + pg * BS * 128, tm, &full[slot], s * 64, y,
+                            pol_kv);
+            }
           }
-        }
-      } else if (lane == 0) {
+        } else if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < kSub; ++s)
-          tma_load_2d(dst + s * L::kSubBytes, tm, &full[slot], kvh * HD + s * 64,
-                      seq_q_begin + j * kPfN, pol_kv);
+          for (int s = 0; s < kSub; ++s)
+            tma_load_2d(dst + s * L::kSubBytes, tm, &full[slot], kvh * HD + s * 64,
+                        it.seq_q_begin + j * kPfN, pol_kv);
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfM, kPfN, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true);
-      auto wait_item = [&](int i) {
-        mbar_wait(&full[i % kSlots], (i / kSlots) & 1, abort_flag, p.err_word);
-        tc_fence_after_sync();
-      };
-      auto release_item = [&](int i) { umma_commit(&empty[i % kSlots]); };
-      auto issue_qk = [&](int w, int j) {   // S_w = Q_w K_j^T
-        const uint32_t q_addr = smem_u32(q_smem + w * L::kTileBytes);
-        const uint32_t k_addr = smem_u32(ring + ((2 * j) % kSlots) * L::kTileBytes);
-        const uint32_t d = tmem_base + w * kPfN;
+    // The whole warp walks the schedule (so addresses and descriptors stay warp-uniform);
+    // lane 0 issues.  Descriptor words are built once per tile: the k-step only adds a
+    // constant to the low word, so consecutive tcgen05.mma are a couple of instructions apart.
+    constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfM, kPfN, false, false);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true);
+    // high descriptor word: SBO = 1024 B, descriptor version 1, 128-byte swizzle
+    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    constexpr uint32_t kLboV = (static_cast<uint32_t>(L::kSubBytes) >> 4) << 16;  // V: next 64 d
+    constexpr uint32_t kLboK = 1u << 16;                                          // unused field
+    const bool leader = lane == 0;
+    auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+    uint32_t ring_base = 0;            // ring index of K_0 of the current item
+    uint32_t item_n = 0;
+    uint32_t tiles_done[kPfQTiles] = {0, 0};   // KV tiles finished per query tile (all items)
+    uint32_t items_done[kPfQTiles] = {0, 0};   // items in which the query tile was active
+    auto wait_ring = [&](uint32_t i) {
+      mbar_wait(&full[i % kSlots], (i / kSlots) & 1, abort_flag, p.err_word);
+      tc_fence_after_sync();
+    };
+    auto release_ring = [&](uint32_t i) {
+      if (leader) umma_commit(&empty[i % kSlots]);
+    };
+    auto issue_qk = [&](int w, uint32_t k_ring) {   // S_w = Q_w K^T
+      const uint32_t q_lo = (smem_u32(q_smem + w * L::kTileBytes) >> 4) | kLboK;
+      const uint32_t k_lo = (smem_u32(ring + (k_ring % kSlots) * L::kTileBytes) >> 4) | kLboK;
+      const uint32_t d = tmem_base + w * kPfN;
+      if (leader) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * L::kSubBytes + (kk & 3) * 32;
-          umma_ss(d, umma_smem_desc_sw128(q_addr + off, 16, 1024),
-                  umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0);
+          const uint32_t off = ((kk >> 2) * L::kSubBytes + (kk & 3) * 32) >> 4;
+          umma_ss(d, desc(q_lo + off), desc(k_lo + off), idesc_qk, kk > 0);
         }
         umma_commit(&s_full[w]);
-      };
-      auto issue_pv = [&](int w, int j) {   // O_w += P_w V_j
-        mbar_wait(&p_full[w], j & 1, abort_flag, p.err_word);
-        tc_fence_after_sync();
-        const uint32_t p_addr = smem_u32(p_smem + w * L::kPBytes);
-        const uint32_t v_addr = smem_u32(ring + ((2 * j + 1) % kSlots) * L::kTileBytes);
-        const uint32_t d = tmem_base + 256 + w * 128;
+      }
+    };
+    auto issue_pv = [&](int w, int j, uint32_t v_ring) {   // O_w (+)= P_w V_j
+      mbar_wait(&p_full[w], tiles_done[w] & 1, abort_flag, p.err_word);
+      if (j == 0)   // O_w of the previous item must have been read out before it is overwritten
+        mbar_wait(&o_empty[w], (items_done[w] & 1) ^ 1, abort_flag, p.err_word);
+      tc_fence_after_sync();
+      const uint32_t p_tmem = tmem_base + w * kPfN;   // P over the first 64 columns of S_w
+      const uint32_t v_lo = (smem_u32(ring + (v_ring % kSlots) * L::kTileBytes) >> 4) | kLboV;
+      const uint32_t d = tmem_base + 256 + w * 128;
+      if (leader) {
 #pragma unroll
         for (int kk = 0; kk < kPfN / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * L::kSubBytes + (kk & 3) * 32;
-          umma_ss(d, umma_smem_desc_sw128(p_addr + a_off, 16, 1024),
-                  umma_smem_desc_sw128(v_addr + kk * 2048, L::kSubBytes, 1024), idesc_pv,
+          // A: 16 keys = 8 packed 32-bit columns per step; B: 16 keys = 2048 B further on
+          umma_ts(d, p_tmem + kk * 8, desc(v_lo + kk * (2048 >> 4)), idesc_pv,
                   (j > 0) || (kk > 0));
         }
         umma_commit(&pv_done[w]);
-      };
-      mbar_wait(q_full, 0, abort_flag, p.err_word);
-      wait_item(0);
+      }
+      ++tiles_done[w];
+    };
+    for (int round = 0;; ++round) {
+      const int item = prefill_item_of(round, blockIdx.x, gridDim.x);
+      if (round * static_cast<int>(gridDim.x) >= p.total_items) break;
+      if (item >= p.total_items) continue;
+      PrefillItem it;
+      if (!prefill_decode_item(p, cu, item, it)) continue;
+      mbar_wait(q_full, item_n & 1, abort_flag, p.err_word);
+      ++item_n;
+      wait_ring(ring_base);                         // K_0
 #pragma unroll
       for (int w = 0; w < kPfQTiles; ++w)
-        if (n_tiles[w] > 0) issue_qk(w, 0);
-      release_item(0);
-      for (int j = 0; j < n_max; ++j) {
-        wait_item(2 * j + 1);                       // V_j
-        const bool has_next = j + 1 < n_max;
+        if (it.n_tiles[w] > 0) issue_qk(w, ring_base);
+      release_ring(ring_base);
+      if (it.n_max == 1 && leader) umma_commit(q_empty);
+      for (int j = 0; j < it.n_max; ++j) {
+        wait_ring(ring_base + 2 * j + 1);           // V_j
+        const bool has_next = j + 1 < it.n_max;
         bool next_k_ready = false;
 #pragma unroll
         for (int w = 0; w < kPfQTiles; ++w) {
-          if (j < n_tiles[w]) {
-            issue_pv(w, j);
-            if (j + 1 < n_tiles[w]) {
+          if (j < it.n_tiles[w]) {
+            issue_pv(w, j, ring_base + 2 * j + 1);
+            if (j + 1 < it.n_tiles[w]) {
               if (!next_k_ready) {
-                wait_item(2 * j + 2);               // K_{j+1}
+                wait_ring(ring_base + 2 * j + 2);   // K_{j+1}
                 next_k_ready = true;
               }
-              issue_qk(w, j + 1);
+              issue_qk(w, ring_base + 2 * j + 2);
             }
           }
         }
-        release_item(2 * j + 1);
-        if (has_next) release_item(2 * j + 2);
+        release_ring(ring_base + 2 * j + 1);
+        if (has_next) {
+          release_ring(ring_base + 2 * j + 2);
+          // the last QK of the item has been issued: Q is free once it retires
+          if (j + 2 == it.n_max && leader) umma_commit(q_empty);
+        }
       }
+#pragma unroll
+      for (int w = 0; w < kPfQTiles; ++w)
+        if (it.n_tiles[w] > 0) ++items_done[w];
+      ring_base += 2 * it.n_max;
     }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
@@ -278,86 +387,80 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_addr = tmem_base + w * kPfN + lane_addr;
     const uint32_t o_addr = tmem_base + 256 + w * 128 + lane_addr;
-    const int q_pos = first_pos[w] + row;
-    const int my_tiles = n_tiles[w];
     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-    float m_run = -INFINITY, l_run = 0.f;
-    for (int j = 0; j < my_tiles; ++j) {
-      mbar_wait(&s_full[w], j & 1, abort_flag, p.err_word);
-      tc_fence_after_sync();
-      uint32_t sreg[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
-      tmem_wait_ld();
-
-      const int key0 = j * kPfN;
-      if (key0 + kPfN - 1 > first_pos[w]) {     // tile crosses the diagonal for some row
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int k = 0; k < 32; ++k)
-            if (key0 + c * 32 + k > q_pos) sreg[c][k] = 0xff800000u;   // -inf
-      }
-      // row max of the raw scores (scale > 0), four independent chains
-      float mx[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        mx[c] = max3(__uint_as_float(sreg[c][0]), __uint_as_float(sreg[c][1]),
-                     __uint_as_float(sreg[c][2]));
-#pragma unroll
-        for (int k = 3; k + 1 < 32; k += 2)
-          mx[c] = max3(mx[c], __uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1]));
-        mx[c] = fmaxf(mx[c], __uint_as_float(sreg[c][31]));
-      }
-      const float mx_s = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
-      float m_new = m_run;
-      if (mx_s - m_run > kPfRescaleThreshold) m_new = mx_s;   // also taken when m_run = -inf
-      const float corr = fast_exp2(m_run - m_new);
-      const bool rescale = (m_new != m_run) && (j > 0);
-      m_run = m_new;
-      if (j > 0) {
-        // PV_{j-1} must have retired before P is overwritten or O is rescaled.  It was issued
-        // before QK_j, whose completion s_full just signalled, so this wait does not block.
-        mbar_wait(&pv_done[w], (j - 1) & 1, abort_flag, p.err_word);
+    uint32_t tiles_done = 0;            // KV tiles this warpgroup has finished (all items)
+    for (int round = 0;; ++round) {
+      const int item = prefill_item_of(round, blockIdx.x, gridDim.x);
+      if (round * static_cast<int>(gridDim.x) >= p.total_items) break;
+      if (item >= p.total_items) continue;
+      PrefillItem it;
+      if (!prefill_decode_item(p, cu, item, it)) continue;
+      const int my_tiles = it.n_tiles[w];
+      if (my_tiles == 0) continue;
+      const int q_pos = it.first_pos[w] + row;
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < my_tiles; ++j, ++tiles_done) {
+        mbar_wait(&s_full[w], tiles_done & 1, abort_flag, p.err_word);
         tc_fence_after_sync();
-      }
-      // p = 2^(s*scale - m): packed FMA, then ex2; two packed running sums.  Each 32-key chunk
-      // goes straight to the swizzled K-major P tile (16-byte piece jj covers keys jj*8..+7).
-      const uint64_t negm2 = pack_f32x2(-m_new, -m_new);
-      const uint32_t p_row = smem_u32(p_smem + w * L::kPBytes) + row * 128;
-      uint64_t sum2[2] = {0ull, 0ull};
+        uint32_t sreg[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t preg[16];
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
+        tmem_wait_ld();
+
+        const int key0 = j * kPfN;
+        if (key0 + kPfN - 1 > it.first_pos[w]) {   // tile crosses the diagonal for some row
 #pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          const uint64_t x2 = fma_f32x2(
-              pack_f32x2(__uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1])), scale2,
-              negm2);
-          float x0, x1;
-          unpack_f32x2(x2, x0, x1);
-          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-          sum2[(k >> 1) & 1] = add_f32x2(sum2[(k >> 1) & 1], pack_f32x2(e0, e1));
-          preg[k >> 1] = pack_bf16x2(e0, e1);
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              if (key0 + c * 32 + k > q_pos) sreg[c][k] = 0xff800000u;   // -inf
         }
+        // row max of the raw scores (scale > 0), four independent chains
+        float mx[4];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int jj = c * 4 + q4;
-          const uint32_t a = p_row + (jj >> 3) * L::kSubBytes + (((jj & 7) ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(preg[q4 * 4]),
-                       "r"(preg[q4 * 4 + 1]), "r"(preg[q4 * 4 + 2]), "r"(preg[q4 * 4 + 3])
-                       : "memory");
+        for (int c = 0; c < 4; ++c) {
+          mx[c] = max3(__uint_as_float(sreg[c][0]), __uint_as_float(sreg[c][1]),
+                       __uint_as_float(sreg[c][2]));
+#pragma unroll
+          for (int k = 3; k + 1 < 32; k += 2)
+            mx[c] = max3(mx[c], __uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1]));
+          mx[c] = fmaxf(mx[c], __uint_as_float(sreg[c][31]));
         }
-      }
-      {
-        float a0, a1, b0, b1;
-        unpack_f32x2(sum2[0], a0, a1);
-        unpack_f32x2(sum2[1], b0, b1);
-        l_run = l_run * corr + ((a0 + a1) + (b0 + b1));
-      }
-      // O row rescale (rare: only when the running max moved by more than the threshold).
-      if (j > 0) {
-        if (__any_sync(0xffffffffu, rescale)) {
+        const float mx_s = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        float m_new = m_run;
+        if (mx_s - m_run > kPfRescaleThreshold) m_new = mx_s;   // also taken when m_run = -inf
+        const float corr = fast_exp2(m_run - m_new);
+        const bool rescale = (m_new != m_run) && (j > 0);
+        m_run = m_new;
+        // p = 2^(s*scale - m): packed FMA, then ex2; two packed running sums.  Each 32-key
+        // chunk goes straight back to tensor memory as 16 packed bf16x2 columns.  QK_j has
+        // retired (s_full), and PV_{j-1} was issued before it, so S_w / P_w / O_w are quiescent.
+        const uint64_t negm2 = pack_f32x2(-m_new, -m_new);
+        uint64_t sum2[2] = {0ull, 0ull};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t preg[16];
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            const uint64_t x2 = fma_f32x2(
+                pack_f32x2(__uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1])), scale2,
+                negm2);
+            float x0, x1;
+            unpack_f32x2(x2, x0, x1);
+            const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+            sum2[(k >> 1) & 1] = add_f32x2(sum2[(k >> 1) & 1], pack_f32x2(e0, e1));
+            preg[k >> 1] = pack_bf16x2(e0, e1);
+          }
+          tmem_st_32x16(s_addr + c * 16, preg);
+        }
+        {
+          float a0, a1, b0, b1;
+          unpack_f32x2(sum2[0], a0, a1);
+          unpack_f32x2(sum2[1], b0, b1);
+          l_run = l_run * corr + ((a0 + a1) + (b0 + b1));
+        }
+        // O row rescale (rare: only when the running max moved by more than the threshold).
+        if (j > 0 && __any_sync(0xffffffffu, rescale)) {
           const float f = rescale ? corr : 1.f;
           const uint64_t f2 = pack_f32x2(f, f);
 #pragma unroll
@@ -375,41 +478,37 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             tmem_st_32x32(o_addr + c * 32, oreg);
           }
-          tmem_wait_st();
         }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&p_full[w]);
       }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(&p_full[w]);
-    }
-    // ---- epilogue: O / l -> bf16 rows
-    if (my_tiles > 0) {
-      mbar_wait(&pv_done[w], (my_tiles - 1) & 1, abort_flag, p.err_word);
+      // ---- item epilogue: O / l -> bf16 rows.  O_w is handed back to the MMA warp as soon as
+      // it sits in registers, so PV_0 of the next item does not wait for the global stores.
+      mbar_wait(&pv_done[w], (tiles_done - 1) & 1, abort_flag, p.err_word);
       tc_fence_after_sync();
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow =
-          p.out + static_cast<int64_t>(seq_q_begin + q0 + w * kPfM + row) * p.out_row_stride +
-          static_cast<int64_t>(head) * HD;
+          p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + w * kPfM + row) * p.out_row_stride +
+          static_cast<int64_t>(it.head) * HD;
+      uint32_t packed[HD / 2];
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t oreg[32];
         tmem_ld_32x32(o_addr + c * 32, oreg);
         tmem_wait_ld();
-        if (row < rows_valid[w]) {
 #pragma unroll
-          for (int k = 0; k < 32; k += 8) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(oreg[k]) * inv_l,
-                              __uint_as_float(oreg[k + 1]) * inv_l);
-            v.y = pack_bf16x2(__uint_as_float(oreg[k + 2]) * inv_l,
-                              __uint_as_float(oreg[k + 3]) * inv_l);
-            v.z = pack_bf16x2(__uint_as_float(oreg[k + 4]) * inv_l,
-                              __uint_as_float(oreg[k + 5]) * inv_l);
-            v.w = pack_bf16x2(__uint_as_float(oreg[k + 6]) * inv_l,
-                              __uint_as_float(oreg[k + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + k) = v;
-          }
-        }
+        for (int k = 0; k < 32; k += 2)
+          packed[(c * 32 + k) >> 1] = pack_bf16x2(__uint_as_float(oreg[k]) * inv_l,
+                                                  __uint_as_float(oreg[k + 1]) * inv_l);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&o_empty[w]);
+      if (row < it.rows_valid[w]) {
+#pragma unroll
+        for (int k = 0; k < HD / 2; k += 4)
+          *reinterpret_cast<uint4*>(orow + 2 * k) =
+              make_uint4(packed[k], packed[k + 1], packed[k + 2], packed[k + 3]);
       }
     }
   }
