@@ -505,9 +505,7 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* 
 int b200attn_debug_read_prefill_trace(long long* out_host, int n) {
   return static_cast<int>(cudaMemcpyFromSymbol(out_host, g_pf_trace, sizeof(long long) * n));
 }
-int b200attn_debug_read_prefill_cta_trace(long long* out_host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out_host, g_pf_cta, sizeof(long long) * n));
-}
+
 #endif
 
 int b200attn_read_error_word(int32_t* out_host, void* stream) {

@@ -28,6 +28,18 @@
 
 namespace b200attn {
 
+#ifdef B200ATTN_PREFILL_TRACE
+// Debug build only: globaltimer stamps per (CTA 0, item, role).
+__device__ long long g_pf_trace[8192];
+#define PF_T(role, item_n, k)                                                              \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && (item_n) < 16)                                                  \
+      g_pf_trace[(role) * 2048 + (item_n) * 16 + (k)] = (long long)global_timer_ns();       \
+  } while (0)
+#else
+#define PF_T(role, item_n, k) do {} while (0)
+#endif
+
 constexpr int kPfM = 128;        // query rows per tile
 constexpr int kPfQTiles = 2;     // query tiles per item
 constexpr int kPfRowsPerItem = kPfM * kPfQTiles;
@@ -36,6 +48,7 @@ constexpr int kPfThreads = 320;
 constexpr float kPfRescaleThreshold = 8.f;  // log2 units
 constexpr int kPfSeqCache = 2048;           // sequences whose cu_q is cached in shared memory
 constexpr int kPfLevelOrderMaxSeqs = 64;    // above this, items keep plain sequence order
+constexpr int kPfItemTable = 96;            // rounds whose item is decoded once, up front
 
 struct PrefillParams {
   __nv_bfloat16* out;
@@ -65,11 +78,20 @@ struct PrefillSmem {
   static constexpr int kQOff = 0;
   static constexpr int kRingOff = kPfQTiles * kTileBytes;
   static constexpr int kSeqOff = kRingOff + kSlots * kTileBytes;
-  static constexpr int kBarOff = kSeqOff + (kPfSeqCache + 2) * 4;
+  static constexpr int kItemOff = kSeqOff + (kPfSeqCache + 2) * 4;
+  static constexpr int kBarOff = kItemOff + kPfItemTable * 16;
   static constexpr int kNumBars = 2 + 2 * kSlots + 4 * kPfQTiles;
   static constexpr int kTotalBytes = kBarOff + kNumBars * 8 + 16 + 1024;
   static_assert(kBarOff % 8 == 0, "barrier alignment");
   static_assert(kTotalBytes <= 232448, "shared memory budget");
+};
+
+// Compact result of the item-order search (one per round, kept in shared memory).
+struct PrefillItemKey {
+  int seq;    // -1 = no such item
+  int q0;
+  int head;
+  int start;
 };
 
 // What every role needs to know about one work item.
@@ -81,10 +103,14 @@ struct PrefillItem {
 
 // Item index -> (sequence, 256-row block, head).  `cu` is cu_q (shared-memory copy when the
 // batch fits the cache).  Heaviest first: blocks ranked by their index inside their sequence,
-// highest first across sequences; the heads of one block are adjacent.
-__device__ __forceinline__ bool prefill_decode_item(const PrefillParams& p, const int32_t* cu,
-                                                    int item, PrefillItem& it) {
-  it.head = item % p.num_q_heads;
+// highest first across sequences; the heads of one block are adjacent.  The search costs
+// microseconds, so the kernel runs it once per round up front (one thread per round) and the
+// roles read the result from shared memory.
+__device__ __forceinline__ PrefillItemKey prefill_find_item(const PrefillParams& p,
+                                                           const int32_t* cu, int item) {
+  PrefillItemKey key{-1, 0, 0, 0};
+  if (item >= p.total_items) return key;
+  key.head = item % p.num_q_heads;
   const int t = item / p.num_q_heads;
   auto nblk = [&](int s) { return (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem; };
   int seq = -1, blk = 0;
@@ -96,7 +122,7 @@ __device__ __forceinline__ bool prefill_decode_item(const PrefillParams& p, cons
       for (int s = 0; s < p.num_seqs; ++s) n += max(0, nblk(s) - r);
       return n;
     };
-    if (max_n == 0 || t >= at_or_above(0)) return false;
+    if (max_n == 0 || t >= at_or_above(0)) return key;
     int lo = 0, hi = max_n - 1;       // largest r with at_or_above(r) > t
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
@@ -125,12 +151,22 @@ __device__ __forceinline__ bool prefill_decode_item(const PrefillParams& p, cons
       acc += n;
     }
   }
-  if (seq < 0) return false;
-  it.seq = seq;
-  it.q0 = blk * kPfRowsPerItem;
-  it.seq_q_begin = cu[seq];
-  it.seq_len_q = cu[seq + 1] - cu[seq];
-  it.start = p.q_start ? p.q_start[seq] : 0;
+  if (seq < 0) return key;
+  key.seq = seq;
+  key.q0 = blk * kPfRowsPerItem;
+  key.start = p.q_start ? p.q_start[seq] : 0;
+  return key;
+}
+
+__device__ __forceinline__ bool prefill_expand_item(const PrefillItemKey& key, const int32_t* cu,
+                                                    PrefillItem& it) {
+  if (key.seq < 0) return false;
+  it.seq = key.seq;
+  it.head = key.head;
+  it.q0 = key.q0;
+  it.start = key.start;
+  it.seq_q_begin = cu[key.seq];
+  it.seq_len_q = cu[key.seq + 1] - it.seq_q_begin;
 #pragma unroll
   for (int w = 0; w < kPfQTiles; ++w) {
     it.rows_valid[w] = max(0, min(kPfM, it.seq_len_q - it.q0 - w * kPfM));
@@ -162,6 +198,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint8_t* q_smem = smem + L::kQOff;
   uint8_t* ring = smem + L::kRingOff;
   int32_t* cu_smem = reinterpret_cast<int32_t*>(smem + L::kSeqOff);
+  PrefillItemKey* item_table = reinterpret_cast<PrefillItemKey*>(smem + L::kItemOff);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* q_full = bars;                   // Q tiles of the item landed (TMA -> MMA)
   uint64_t* q_empty = bars + 1;              // last QK of the item retired (MMA -> TMA)
@@ -184,6 +221,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   if (cu_cached)
     for (int s = threadIdx.x; s <= p.num_seqs; s += blockDim.x) cu_smem[s] = p.cu_q[s];
   const int32_t* cu = cu_cached ? cu_smem : p.cu_q;
+  if (cu_cached) __syncthreads();
+  const int num_rounds = (p.total_items + gridDim.x - 1) / gridDim.x;
+  for (int r = threadIdx.x; r < min(num_rounds, kPfItemTable); r += blockDim.x)
+    item_table[r] = prefill_find_item(p, cu, prefill_item_of(r, blockIdx.x, gridDim.x));
+  auto get_item = [&](int round, PrefillItem& it) {
+    const PrefillItemKey key =
+        round < kPfItemTable ? item_table[round]
+                             : prefill_find_item(p, cu, prefill_item_of(round, blockIdx.x, gridDim.x));
+    return prefill_expand_item(key, cu, it);
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -221,12 +268,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint64_t pol_q = l2_policy_evict_first();
     const uint64_t pol_kv = l2_policy_evict_last();
     uint32_t ring_i = 0, item_n = 0;
-    for (int round = 0;; ++round) {
-      const int item = prefill_item_of(round, blockIdx.x, gridDim.x);
-      if (round * static_cast<int>(gridDim.x) >= p.total_items) break;
-      if (item >= p.total_items) continue;
+    for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
-      if (!prefill_decode_item(p, cu, item, it)) continue;
+      if (!get_item(round, it)) continue;
       const int kvh = it.head / p.group;
       // Q may be overwritten once every QK of the previous item has retired.
       mbar_wait(q_empty, (item_n & 1) ^ 1, abort_flag, p.err_word);
@@ -337,15 +381,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       ++tiles_done[w];
     };
-    for (int round = 0;; ++round) {
-      const int item = prefill_item_of(round, blockIdx.x, gridDim.x);
-      if (round * static_cast<int>(gridDim.x) >= p.total_items) break;
-      if (item >= p.total_items) continue;
+    for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
-      if (!prefill_decode_item(p, cu, item, it)) continue;
+      if (!get_item(round, it)) continue;
+      if (leader) PF_T(0, item_n, 0);
       mbar_wait(q_full, item_n & 1, abort_flag, p.err_word);
+      if (leader) PF_T(0, item_n, 1);
       ++item_n;
       wait_ring(ring_base);                         // K_0
+      if (leader) PF_T(0, item_n - 1, 2);
 #pragma unroll
       for (int w = 0; w < kPfQTiles; ++w)
         if (it.n_tiles[w] > 0) issue_qk(w, ring_base);
@@ -378,6 +422,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
       for (int w = 0; w < kPfQTiles; ++w)
         if (it.n_tiles[w] > 0) ++items_done[w];
+      if (leader) PF_T(0, item_n - 1, 3);
       ring_base += 2 * it.n_max;
     }
   } else {
@@ -389,19 +434,20 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t o_addr = tmem_base + 256 + w * 128 + lane_addr;
     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
     uint32_t tiles_done = 0;            // KV tiles this warpgroup has finished (all items)
-    for (int round = 0;; ++round) {
-      const int item = prefill_item_of(round, blockIdx.x, gridDim.x);
-      if (round * static_cast<int>(gridDim.x) >= p.total_items) break;
-      if (item >= p.total_items) continue;
+    for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
-      if (!prefill_decode_item(p, cu, item, it)) continue;
+      if (!get_item(round, it)) continue;
       const int my_tiles = it.n_tiles[w];
       if (my_tiles == 0) continue;
       const int q_pos = it.first_pos[w] + row;
       float m_run = -INFINITY, l_run = 0.f;
+      const bool tr = (warp == 2 + 4 * w) && lane == 0;
+      (void)tr;
+      if (tr) PF_T(1 + w, round, 0);
       for (int j = 0; j < my_tiles; ++j, ++tiles_done) {
         mbar_wait(&s_full[w], tiles_done & 1, abort_flag, p.err_word);
         tc_fence_after_sync();
+        if (tr && j == 0) PF_T(1 + w, round, 1);
         uint32_t sreg[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
@@ -485,25 +531,31 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       // ---- item epilogue: O / l -> bf16 rows.  O_w is handed back to the MMA warp as soon as
       // it sits in registers, so PV_0 of the next item does not wait for the global stores.
+      if (tr) PF_T(1 + w, round, 2);
       mbar_wait(&pv_done[w], (tiles_done - 1) & 1, abort_flag, p.err_word);
       tc_fence_after_sync();
+      if (tr) PF_T(1 + w, round, 3);
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow =
           p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + w * kPfM + row) * p.out_row_stride +
           static_cast<int64_t>(it.head) * HD;
-      uint32_t packed[HD / 2];
+      uint32_t oreg[HD / 32][32];
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t oreg[32];
-        tmem_ld_32x32(o_addr + c * 32, oreg);
-        tmem_wait_ld();
-#pragma unroll
-        for (int k = 0; k < 32; k += 2)
-          packed[(c * 32 + k) >> 1] = pack_bf16x2(__uint_as_float(oreg[k]) * inv_l,
-                                                  __uint_as_float(oreg[k + 1]) * inv_l);
-      }
+      for (int c = 0; c < HD / 32; ++c) tmem_ld_32x32(o_addr + c * 32, oreg[c]);
+      tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&o_empty[w]);
+      if (tr) PF_T(1 + w, round, 4);
+#ifdef B200ATTN_PREFILL_TRACE
+      if (tr && blockIdx.x == 0 && round < 16) g_pf_trace[(1 + w) * 2048 + round * 16 + 6] = my_tiles;
+#endif
+      uint32_t packed[HD / 2];
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c)
+#pragma unroll
+        for (int k = 0; k < 32; k += 2)
+          packed[(c * 32 + k) >> 1] = pack_bf16x2(__uint_as_float(oreg[c][k]) * inv_l,
+                                                  __uint_as_float(oreg[c][k + 1]) * inv_l);
       if (row < it.rows_valid[w]) {
 #pragma unroll
         for (int k = 0; k < HD / 2; k += 4)
