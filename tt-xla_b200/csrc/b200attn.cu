@@ -500,14 +500,6 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* 
                                B200ATTN_STATIC_WORKSPACE_BYTES, stream);
 }
 
-#ifdef B200ATTN_PREFILL_TRACE
-// Debug build only: copies the prefill trace stamps to the host.
-int b200attn_debug_read_prefill_trace(long long* out_host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out_host, g_pf_trace, sizeof(long long) * n));
-}
-
-#endif
-
 int b200attn_read_error_word(int32_t* out_host, void* stream) {
   if (!out_host) return B200ATTN_ERR_NULL_POINTER;
   DeviceInfo* dev;

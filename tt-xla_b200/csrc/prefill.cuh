@@ -28,18 +28,6 @@
 
 namespace b200attn {
 
-#ifdef B200ATTN_PREFILL_TRACE
-// Debug build only: globaltimer stamps per (CTA 0, item, role).
-__device__ long long g_pf_trace[8192];
-#define PF_T(role, item_n, k)                                                              \
-  do {                                                                                     \
-    if (blockIdx.x == 0 && (item_n) < 16)                                                  \
-      g_pf_trace[(role) * 2048 + (item_n) * 16 + (k)] = (long long)global_timer_ns();       \
-  } while (0)
-#else
-#define PF_T(role, item_n, k) do {} while (0)
-#endif
-
 constexpr int kPfM = 128;        // query rows per tile
 constexpr int kPfQTiles = 2;     // query tiles per item
 constexpr int kPfRowsPerItem = kPfM * kPfQTiles;
@@ -78,10 +66,11 @@ struct PrefillSmem {
   static constexpr int kQOff = 0;
   static constexpr int kRingOff = kPfQTiles * kTileBytes;
   static constexpr int kSeqOff = kRingOff + kSlots * kTileBytes;
-  static constexpr int kItemOff = kSeqOff + (kPfSeqCache + 2) * 4;
+  static constexpr int kItemOff = kSeqOff + (kPfSeqCache + 4) * 4;   // keeps 16-byte alignment
   static constexpr int kBarOff = kItemOff + kPfItemTable * 16;
   static constexpr int kNumBars = 2 + 2 * kSlots + 4 * kPfQTiles;
   static constexpr int kTotalBytes = kBarOff + kNumBars * 8 + 16 + 1024;
+  static_assert(kItemOff % 16 == 0, "16-byte vector access alignment");
   static_assert(kBarOff % 8 == 0, "barrier alignment");
   static_assert(kTotalBytes <= 232448, "shared memory budget");
 };
@@ -384,12 +373,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
       if (!get_item(round, it)) continue;
-      if (leader) PF_T(0, item_n, 0);
       mbar_wait(q_full, item_n & 1, abort_flag, p.err_word);
-      if (leader) PF_T(0, item_n, 1);
       ++item_n;
       wait_ring(ring_base);                         // K_0
-      if (leader) PF_T(0, item_n - 1, 2);
 #pragma unroll
       for (int w = 0; w < kPfQTiles; ++w)
         if (it.n_tiles[w] > 0) issue_qk(w, ring_base);
@@ -422,7 +408,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
       for (int w = 0; w < kPfQTiles; ++w)
         if (it.n_tiles[w] > 0) ++items_done[w];
-      if (leader) PF_T(0, item_n - 1, 3);
       ring_base += 2 * it.n_max;
     }
   } else {
@@ -441,13 +426,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (my_tiles == 0) continue;
       const int q_pos = it.first_pos[w] + row;
       float m_run = -INFINITY, l_run = 0.f;
-      const bool tr = (warp == 2 + 4 * w) && lane == 0;
-      (void)tr;
-      if (tr) PF_T(1 + w, round, 0);
       for (int j = 0; j < my_tiles; ++j, ++tiles_done) {
         mbar_wait(&s_full[w], tiles_done & 1, abort_flag, p.err_word);
         tc_fence_after_sync();
-        if (tr && j == 0) PF_T(1 + w, round, 1);
         uint32_t sreg[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
@@ -531,24 +512,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       // ---- item epilogue: O / l -> bf16 rows.  O_w is handed back to the MMA warp as soon as
       // it sits in registers, so PV_0 of the next item does not wait for the global stores.
-      if (tr) PF_T(1 + w, round, 2);
       mbar_wait(&pv_done[w], (tiles_done - 1) & 1, abort_flag, p.err_word);
       tc_fence_after_sync();
-      if (tr) PF_T(1 + w, round, 3);
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow =
-          p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + w * kPfM + row) * p.out_row_stride +
-          static_cast<int64_t>(it.head) * HD;
       uint32_t oreg[HD / 32][32];
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) tmem_ld_32x32(o_addr + c * 32, oreg[c]);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&o_empty[w]);
-      if (tr) PF_T(1 + w, round, 4);
-#ifdef B200ATTN_PREFILL_TRACE
-      if (tr && blockIdx.x == 0 && round < 16) g_pf_trace[(1 + w) * 2048 + round * 16 + 6] = my_tiles;
-#endif
       uint32_t packed[HD / 2];
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c)
@@ -557,6 +529,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           packed[(c * 32 + k) >> 1] = pack_bf16x2(__uint_as_float(oreg[c][k]) * inv_l,
                                                   __uint_as_float(oreg[c][k + 1]) * inv_l);
       if (row < it.rows_valid[w]) {
+        __nv_bfloat16* orow =
+            p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + w * kPfM + row) * p.out_row_stride +
+            static_cast<int64_t>(it.head) * HD;
 #pragma unroll
         for (int k = 0; k < HD / 2; k += 4)
           *reinterpret_cast<uint4*>(orow + 2 * k) =
