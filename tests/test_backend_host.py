@@ -1,0 +1,109 @@
+"""Host-side logic of the backend mirror (no GPU): descriptors, page accounting, argument checks,
+varlen metadata derivation."""
+import pytest
+import torch
+
+from b200attn import (B200AttentionBackend, B200AttentionBackendImpl,
+                      B200AttentionMetadataBuilder, B200Metadata, backend, ops)
+
+
+def test_backend_descriptors_match_reference_contract():
+    B = B200AttentionBackend
+    assert B.get_name() == "CUSTOM"
+    assert B.get_impl_cls() is B200AttentionBackendImpl
+    assert B.get_builder_cls() is B200AttentionMetadataBuilder
+    # one of the two separate K / V tensors per layer (attention.py:103-112)
+    assert B.get_kv_cache_shape(512, 32, 8, 64) == (512, 8, 32, 64)
+    assert B.get_fused_kv_cache_shape(512, 32, 8, 64) == (2, 512, 8, 32, 64)
+    assert B.get_page_size() == 32
+    with pytest.raises(RuntimeError, match="swap_blocks"):
+        B.swap_blocks(None, None, None)
+    # attention.py:137-140
+    assert B.get_max_num_seqs(32768, 32) == 1024 * 1024 // 2 // 1024 // 4
+    assert B.get_min_page_size(32768, 64) == 16
+
+
+def test_page_size_bytes():
+    # attention.py:750-771 arithmetic: 32 tokens x 16 combined heads x 64 x 2 bytes
+    assert backend.get_page_size_bytes(32, 8, 64, torch.bfloat16) == 32 * 16 * 64 * 2
+    # head_size padded to a multiple of 32
+    assert backend.get_page_size_bytes(32, 8, 80, torch.bfloat16) == 32 * 16 * 96 * 2
+    assert backend.get_dtype_packing(torch.bfloat16) == 2
+    assert backend.dtype_bits(torch.int8) == 8
+
+
+def test_metadata_defaults_and_positional_order():
+    pt = torch.zeros(2, 4, dtype=torch.int32)
+    md = B200Metadata(torch.tensor([3, 4], dtype=torch.int32), None, pt, True)
+    assert md.fill_page_table is pt            # attention.py:210-212
+    assert md.dp_size == 1 and md.chunk_start_idx is None and not md.is_varlen
+
+
+def test_impl_constructor_errors():
+    with pytest.raises(NotImplementedError, match="Alibi"):
+        B200AttentionBackendImpl(8, 64, 0.125, 8, [1.0], None, "auto")
+    with pytest.raises(NotImplementedError, match="encoder or decoder"):
+        B200AttentionBackendImpl(8, 64, 0.125, 8, None, None, "auto", attn_type="encoder_decoder")
+    for kw in (dict(sliding_window=128), dict(kv_cache_dtype="fp8"), dict(logits_soft_cap=30.0)):
+        args = dict(num_heads=8, head_size=64, scale=0.125, num_kv_heads=8, alibi_slopes=None,
+                    sliding_window=None, kv_cache_dtype="auto")
+        args.update(kw)
+        with pytest.raises(NotImplementedError):
+            B200AttentionBackendImpl(**args)
+
+
+def test_normalize_shapes_and_messages():
+    impl = B200AttentionBackendImpl(8, 64, 0.125, 2, None, None, "auto")
+    x = torch.zeros(6, 8 * 64)
+    assert impl._normalize_to_attention_format(x, "query", 8, 64, 3).shape == (3, 2, 8, 64)
+    assert impl._normalize_to_attention_format(x.view(6, 8, 64), "query", 8, 64, 2).shape == \
+        (2, 3, 8, 64)
+    with pytest.raises(ValueError, match="rank >= 2"):
+        impl._normalize_to_attention_format(torch.zeros(5), "query", 8, 64, 1)
+    with pytest.raises(ValueError, match="flattened-token tensor"):
+        impl._normalize_to_attention_format(torch.zeros(6, 100), "key", 2, 64, 3)
+    with pytest.raises(ValueError, match="divisible"):
+        impl._normalize_to_attention_format(x, "query", 8, 64, 4)
+    md = B200Metadata(num_users=3)
+    ins = impl._prepare_inputs(x, torch.zeros(6, 2 * 64), torch.zeros(6, 2 * 64), md)
+    assert ins.is_prefill and ins.query_num_tokens == 2 and ins.users == 3
+    with pytest.raises(ValueError, match="key and value must match"):
+        impl._prepare_inputs(x, torch.zeros(6, 2 * 64), torch.zeros(3, 2 * 64), md)
+
+
+def test_forward_requires_metadata_and_output():
+    impl = B200AttentionBackendImpl(8, 64, 0.125, 2, None, None, "auto")
+    x = torch.zeros(2, 512)
+    with pytest.raises(AssertionError, match="requires metadata"):
+        impl.forward(None, x, x, x, None, None, output=x)
+    with pytest.raises(AssertionError, match="output buffer"):
+        impl.forward(None, x, x, x, None, B200Metadata(num_users=2), output=None)
+
+
+def test_ops_refuse_cpu_tensors():
+    kc = torch.zeros(4, 2, 32, 64, dtype=torch.bfloat16)
+    q = torch.zeros(1, 8, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.paged_decode(q, kc, kc, torch.zeros(1, 4, dtype=torch.int32),
+                         torch.zeros(1, dtype=torch.int32))
+
+
+def test_varlen_metadata_from_vllm_fields():
+    # 3 decode rows first (vLLM's order), then a 5-token chunk on a 64-token prefix and a fresh
+    # 7-token prompt
+    qsl = torch.tensor([0, 1, 2, 3, 8, 15], dtype=torch.int32)
+    seq_lens = torch.tensor([10, 20, 30, 69, 7], dtype=torch.int32)
+    md = backend.build_varlen_metadata(qsl, qsl.clone(), seq_lens,
+                                       torch.zeros(5, 4, dtype=torch.int32),
+                                       torch.arange(15, dtype=torch.int64), max_seq_len=69)
+    assert md.is_varlen and md.num_decodes == 3 and md.num_users == 5
+    assert md.decode_cur_pos.tolist() == [9, 19, 29]
+    assert md.prefill_cu_q_cpu.tolist() == [0, 5, 12]
+    assert md.prefill_q_start.tolist() == [64, 0]
+
+
+def test_builder_returns_stub_without_varlen_fields():
+    class Common:
+        causal = True
+    md = B200AttentionMetadataBuilder().build(0, Common())
+    assert isinstance(md, B200Metadata) and md.cache_position is None and md.is_causal
