@@ -39,6 +39,12 @@ for _p in (ROOT, os.path.join(ROOT, "tt-xla_b200")):
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
+# DRAM traffic of the split-KV decode kernel, from the ncu capture of the small config-4 case
+# (profiles/decode_splitkv_c4.md): reads = 268.60 MB for 268.70 MB of algorithmic bytes, writes
+# = 6.25 MB for 8.52 MB of fp32 split partials (the rest is still in L2 when the combine reads
+# it).  Both parts grow in proportion to their own size, so a full launch is scaled from them.
+NCU_READ_PER_ALGORITHMIC_BYTE = 268.60 / 268.70
+NCU_WRITE_PER_PARTIAL_BYTE = 6.25 / 8.52
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -294,7 +300,8 @@ def run_decode_bench(args, wl, rank, world, device):
     ms_per_step = total_ms / args.steps
     return dict(w=w, full_bytes=full_bytes, rank_bytes=rank_bytes, ms_per_step=ms_per_step,
                 decode_ms=decode_ms, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h, clocks=clocks,
-                splits=splits, launches=3 * args.steps)
+                splits=splits, launches=3 * args.steps,
+                partial_bytes=ops.decode_workspace_bytes(users, nq, hd, splits))
 
 
 def run_prefill_bench(args, rank, world, device, peaks):
@@ -479,6 +486,8 @@ def main():
         value = r["full_bytes"] / (r["ms_per_step"] * 1e-3) / 1e9
         e2e = r["full_bytes"] / (r["e2e_ms"] * 1e-3) / 1e9
         achieved = r["rank_bytes"] / (r["decode_ms"] * 1e-3) / 1e9
+        traffic = int(r["rank_bytes"] * NCU_READ_PER_ALGORITHMIC_BYTE
+                      + r["partial_bytes"] * NCU_WRITE_PER_PARTIAL_BYTE)
         line = {
             "metric": "decode_attn_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -496,7 +505,8 @@ def main():
             "gpu_launches": r["launches"],
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-                         "traffic": None, "peak_source": peaks["source"],
+                         "traffic": traffic, "traffic_source": "ncu capture of the small case, scaled",
+                         "peak_source": peaks["source"],
                          "kernel": "paged_decode_splitkv_kernel + decode_combine_kernel",
                          "ms_per_launch": round(r["decode_ms"], 4),
                          "algorithmic_bytes_per_launch": r["rank_bytes"]},
