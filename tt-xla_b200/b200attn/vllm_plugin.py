@@ -1,0 +1,103 @@
+"""vLLM registration of the B200 attention backend.
+
+The reference plugin registers its backend as `AttentionBackendEnum.CUSTOM` at import
+(integrations/vllm_plugin/vllm_tt/__init__.py:10-17) and is discovered through the
+`vllm.platform_plugins` / `vllm.general_plugins` entry points of its setup.py (:58-61).  Here
+`register()` is the `vllm.general_plugins` entry point (see the `b200attn-*.dist-info` directory
+next to this package): vLLM calls it in every process it starts, so engine core and
+tensor-parallel workers all know the backend.  Select it with `attention_backend="CUSTOM"` and a
+KV block size of 32 or 64.
+
+The classes below only adapt `b200attn.backend` to vLLM's abstract base classes; the attention
+math, the cache layout and the metadata derivation live there.
+"""
+from __future__ import annotations
+
+import torch
+
+from vllm.v1.attention.backend import (AttentionBackend, AttentionImpl, AttentionMetadataBuilder,
+                                       AttentionType)
+
+from . import backend as _b
+
+
+class B200VllmMetadataBuilder(AttentionMetadataBuilder[_b.B200Metadata]):
+    """CommonAttentionMetadata -> B200Metadata, once per step; decode rows are ordered first."""
+
+    reorder_batch_threshold = 1
+
+    def __init__(self, kv_cache_spec, layer_names, vllm_config, device):
+        super().__init__(kv_cache_spec, layer_names, vllm_config, device)
+        self._init_reorder_batch_threshold(1)
+        self._impl = _b.B200AttentionMetadataBuilder(kv_cache_spec, layer_names, vllm_config,
+                                                     device)
+
+    def build(self, common_prefix_len, common_attn_metadata, fast_build: bool = False):
+        return self._impl.build(common_prefix_len, common_attn_metadata, fast_build)
+
+
+class B200VllmAttentionImpl(_b.B200AttentionBackendImpl, AttentionImpl[_b.B200Metadata]):
+    def __init__(self, num_heads, head_size, scale, num_kv_heads=None, alibi_slopes=None,
+                 sliding_window=None, kv_cache_dtype="auto", logits_soft_cap=None,
+                 attn_type=AttentionType.DECODER, kv_sharing_target_layer_name=None, **extra):
+        _b.B200AttentionBackendImpl.__init__(
+            self, num_heads, head_size, scale,
+            num_kv_heads if num_kv_heads is not None else num_heads, alibi_slopes,
+            sliding_window, kv_cache_dtype, logits_soft_cap, attn_type,
+            kv_sharing_target_layer_name, extra.get("sinks"))
+        self.kv_cache_dtype = kv_cache_dtype
+
+    def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None,
+                output_scale=None, output_block_scale=None):
+        if attn_metadata is None:          # memory-profiling run: no metadata, nothing to attend
+            return output.fill_(0) if output is not None else query.new_zeros(query.shape)
+        return _b.B200AttentionBackendImpl.forward(
+            self, layer, query, key, value, kv_cache, attn_metadata, output, output_scale,
+            output_block_scale)
+
+
+class B200VllmAttentionBackend(AttentionBackend):
+    accept_output_buffer = True
+    forward_includes_kv_cache_update = True
+    supported_dtypes = [torch.bfloat16]
+    supported_kv_cache_dtypes = ["auto", "bfloat16"]
+
+    @staticmethod
+    def get_name() -> str:
+        return "CUSTOM"
+
+    @staticmethod
+    def get_impl_cls():
+        return B200VllmAttentionImpl
+
+    @staticmethod
+    def get_builder_cls():
+        return B200VllmMetadataBuilder
+
+    @staticmethod
+    def get_kv_cache_shape(num_blocks, block_size, num_kv_heads, head_size,
+                           cache_dtype_str: str = "auto"):
+        # vLLM's CUDA runner holds one tensor per layer: index 0 / 1 are the K and V tensors of
+        # the plugin layout (attention.py:103-112).
+        return _b.B200AttentionBackend.get_fused_kv_cache_shape(num_blocks, block_size,
+                                                                num_kv_heads, head_size)
+
+    @staticmethod
+    def get_supported_kernel_block_sizes():
+        return list(_b.B200AttentionBackend.supported_block_sizes)
+
+    @classmethod
+    def get_supported_head_sizes(cls):
+        return list(_b.B200AttentionBackend.supported_head_sizes)
+
+    @classmethod
+    def supports_compute_capability(cls, capability) -> bool:
+        return getattr(capability, "major", 10) == 10
+
+
+def register() -> None:
+    """`vllm.general_plugins` entry point."""
+    from vllm.v1.attention.backends.registry import AttentionBackendEnum, register_backend
+
+    register_backend(AttentionBackendEnum.CUSTOM,
+                     "b200attn.vllm_plugin.B200VllmAttentionBackend")
