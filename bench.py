@@ -354,6 +354,98 @@ def run_prefill_bench(args, rank, world, device, peaks):
                          "peak_source": peaks["source"]}}
 
 
+# ------------------------------------------------------------------------------ config 5
+LLAMA31_8B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=4096,
+                  intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                  num_key_value_heads=8, head_dim=128, vocab_size=128256, rope_theta=500000.0,
+                  max_position_embeddings=8192, rms_norm_eps=1e-5, torch_dtype="bfloat16",
+                  tie_word_embeddings=False, hidden_act="silu", bos_token_id=1, eos_token_id=2)
+
+
+def run_e2e_llama(args):
+    """Config 5: end-to-end decode of a random-init Llama-3.1-8B through vLLM with this
+    repository's backend registered as the CUSTOM attention backend (the way the reference
+    plugin registers its own).  Batch 64, prompts of 1024 uniform-random token ids, 256 output
+    tokens each, greedy, no EOS.  Tensor parallel = number of ranks (torchrun); vLLM's own NCCL
+    all-reduce follows o_proj and down_proj.  Decode steps replay as CUDA graphs."""
+    import tempfile
+
+    pkg = os.path.join(ROOT, "tt-xla_b200")
+    os.environ["PYTHONPATH"] = pkg + os.pathsep + os.environ.get("PYTHONPATH", "")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world > 1:
+        os.environ["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"
+    from vllm import LLM, SamplingParams
+
+    cfg_dir = tempfile.mkdtemp(prefix="llama31_8b_cfg_")
+    with open(os.path.join(cfg_dir, "config.json"), "w") as f:
+        json.dump(LLAMA31_8B, f)
+    batch, prompt_len, gen_len = 64, 1024, 256
+    kw = dict(model=cfg_dir, load_format="dummy", skip_tokenizer_init=True, dtype="bfloat16",
+              block_size=64, max_model_len=2048, max_num_seqs=batch, max_num_batched_tokens=8192,
+              gpu_memory_utilization=0.85, seed=0, enable_prefix_caching=False,
+              tensor_parallel_size=world, enforce_eager=False,
+              compilation_config={"mode": 0, "cudagraph_mode": "FULL_DECODE_ONLY"})
+    if args.attn == "b200":
+        kw["attention_backend"] = "CUSTOM"
+    if world > 1:
+        kw["distributed_executor_backend"] = "external_launcher"
+    llm = LLM(**kw)
+    g = torch.Generator().manual_seed(0)
+    prompts = [dict(prompt_token_ids=torch.randint(0, LLAMA31_8B["vocab_size"], (prompt_len,),
+                                                   generator=g).tolist()) for _ in range(batch)]
+
+    def timed(max_tokens):
+        sp = SamplingParams(max_tokens=max_tokens, ignore_eos=True, temperature=0.0,
+                            detokenize=False)
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, sp, use_tqdm=False)
+        dt = time.perf_counter() - t0
+        return dt, sum(len(o.outputs[0].token_ids) for o in outs)
+
+    timed(8)                                   # warm-up: graphs captured, allocator settled
+    reps = max(1, min(args.steps, 3))
+    t_first = min(timed(1)[0] for _ in range(reps))        # prefill + first token
+    full = [timed(gen_len) for _ in range(reps)]
+    t_full = min(f[0] for f in full)
+    n_tok = full[0][1]
+    decode_s = t_full - t_first
+    decode_tok = batch * (gen_len - 1)
+    tok_s = decode_tok / decode_s
+    # stop the engine first so that its shutdown messages do not follow the result line
+    try:
+        llm.llm_engine.engine_core.shutdown()
+    except Exception:
+        pass
+    del llm
+    time.sleep(1.0)
+    if rank == 0:
+        step_ms = decode_s / (gen_len - 1) * 1e3
+        weights = 2 * (LLAMA31_8B["vocab_size"] * 4096 * 2 + 32 * (4096 * 6144 + 4096 * 4096 +
+                                                                    3 * 4096 * 14336))
+        kv_per_step = batch * (prompt_len + gen_len / 2) * 32 * 2 * 8 * 128 * 2
+        peaks = load_peaks()
+        gbs = (weights + kv_per_step) / world / (step_ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "e2e_decode_tokens_per_s", "value": round(tok_s, 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": reps, "warmup": 1, "ms_per_step": round(step_ms, 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "c5_llama31_8b_e2e_decode_B64_P1024_G256",
+                       "parallelism": f"tp{world}", "attention_backend": args.attn,
+                       "weights": "random init (vLLM dummy loader)",
+                       "timing": "wall clock around LLM.generate; decode = (256-token run) - "
+                                 "(1-token run); decode steps are CUDA-graph replays"},
+            "ttft_s": round(t_first, 4), "generate_s": round(t_full, 4), "tokens": n_tok,
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+                         "traffic": None, "peak_source": peaks["source"],
+                         "note": "per-GPU bytes of one decode step = bf16 weights / TP + mean "
+                                 "KV of the batch / TP"},
+        }), flush=True)
+
+
 # ------------------------------------------------------------------------------ CPU side
 def cpu_decode_sample(wl: dict, n_users: int, seed: int = 0):
     """A bounded sample of the decode workload for the CPU oracle: n_users users of the batch,
@@ -446,13 +538,23 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--attn", default="b200", choices=["b200", "stock"],
+                    help="c5 only: this repository's backend, or vLLM's stock one for comparison")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="prefill: run only the config-2 prefill part (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.workload == "c5":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "config 5 on CPU is not a bounded sample: the reference arm covers "
+                              "the decode-attention workloads"}))
+            return
+        run_e2e_llama(args)
+        return
     wl = WORKLOADS[args.workload]
 
     if args.impl == "reference":

@@ -99,6 +99,11 @@ class B200AttentionMetadataBuilder:
         self.layer_names = layer_names
         self.vllm_config = vllm_config
         self.device = device
+        self.decode_cur_pos_buffer = None
+        max_seqs = getattr(getattr(vllm_config, "scheduler_config", None), "max_num_seqs", None)
+        if max_seqs and device is not None:
+            self.decode_cur_pos_buffer = torch.zeros(int(max_seqs), dtype=torch.int32,
+                                                     device=device)
 
     def build(self, common_prefix_len: int, common_attn_metadata, fast_build: bool = False):
         m = common_attn_metadata
@@ -117,6 +122,7 @@ class B200AttentionMetadataBuilder:
             slot_mapping=m.slot_mapping,
             max_seq_len=int(getattr(m, "max_seq_len", 0) or 0),
             is_causal=getattr(m, "causal", True),
+            decode_cur_pos_buffer=self.decode_cur_pos_buffer,
         )
 
 
@@ -128,9 +134,12 @@ def build_varlen_metadata(
     slot_mapping: torch.Tensor,
     max_seq_len: int = 0,
     is_causal: bool = True,
+    decode_cur_pos_buffer: Optional[torch.Tensor] = None,
 ) -> B200Metadata:
     """Derives the per-kernel index tensors from vLLM's varlen fields.  Rows whose query length
-    is 1 must come first (vLLM's decode-first batch order)."""
+    is 1 must come first (vLLM's decode-first batch order).  `decode_cur_pos_buffer`, when
+    given, is a persistent int32 buffer the decode positions are written into, so that a CUDA
+    graph captured over a decode step keeps reading the right memory on replay."""
     qsl_cpu = query_start_loc_cpu.to(torch.int32)
     q_lens = qsl_cpu[1:] - qsl_cpu[:-1]
     num_seqs = q_lens.numel()
@@ -152,7 +161,11 @@ def build_varlen_metadata(
         num_users=num_seqs,
     )
     if num_decodes > 0:
-        md.decode_cur_pos = (seq_lens[:num_decodes] - 1).contiguous()
+        if decode_cur_pos_buffer is not None and decode_cur_pos_buffer.numel() >= num_decodes:
+            md.decode_cur_pos = decode_cur_pos_buffer[:num_decodes]
+            torch.sub(seq_lens[:num_decodes], 1, out=md.decode_cur_pos)
+        else:
+            md.decode_cur_pos = (seq_lens[:num_decodes] - 1).contiguous()
     if num_decodes < num_seqs:
         base = int(qsl_cpu[num_decodes])
         md.prefill_cu_q_cpu = (qsl_cpu[num_decodes:] - base).contiguous()

@@ -15,8 +15,8 @@ from __future__ import annotations
 
 import torch
 
-from vllm.v1.attention.backend import (AttentionBackend, AttentionImpl, AttentionMetadataBuilder,
-                                       AttentionType)
+from vllm.v1.attention.backend import (AttentionBackend, AttentionCGSupport, AttentionImpl,
+                                       AttentionMetadataBuilder, AttentionType)
 
 from . import backend as _b
 
@@ -25,6 +25,9 @@ class B200VllmMetadataBuilder(AttentionMetadataBuilder[_b.B200Metadata]):
     """CommonAttentionMetadata -> B200Metadata, once per step; decode rows are ordered first."""
 
     reorder_batch_threshold = 1
+    # A pure decode step launches the same three kernels on persistent buffers (slot_mapping,
+    # block table, positions), so it can be captured and replayed as one CUDA graph.
+    _cudagraph_support = AttentionCGSupport.UNIFORM_SINGLE_TOKEN_DECODE
 
     def __init__(self, kv_cache_spec, layer_names, vllm_config, device):
         super().__init__(kv_cache_spec, layer_names, vllm_config, device)
