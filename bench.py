@@ -218,7 +218,7 @@ def run_decode_bench(args, wl, rank, world, device):
     v3 = dev["v"].view(users, nkv, hd)
     out3 = out.view(users, nq, hd)
     scale = hd ** -0.5
-    splits = ops.decode_auto_splits(users, nkv, bs, w["max_ctx"])
+    splits = ops.decode_auto_splits(users, nkv, hd, w["max_ctx"])
 
     def step():
         ops.paged_update_cache(w["k_cache"], w["v_cache"], k3, v3, dev["cache_position"],

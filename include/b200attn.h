@@ -172,9 +172,9 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride,
                                  int block_size, int64_t num_blocks, float scale,
                                  int max_context_len, int num_splits, void* stream);
 
-/* Split count the library would pick for a decode batch (host heuristic, no device access
- * beyond the SM count).  max_context_len <= 0 means "unknown": the page-table width bounds it. */
-int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int block_size,
+/* Split count the library would pick for a decode batch (host cost model fitted to B200
+ * measurements; no device access beyond the SM count).  max_context_len <= 0 means "unknown": the page-table width bounds it. */
+int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
                                 int max_context_len);
 
 /* Bytes of scratch b200attn_paged_decode needs for num_splits splits (0 when num_splits <= 1). */

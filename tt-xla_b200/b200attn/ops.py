@@ -172,8 +172,8 @@ def kv_scatter_slots(
     )
 
 
-def decode_auto_splits(users: int, nkv: int, bs: int, max_context_len: int) -> int:
-    return _lib.lib().b200attn_decode_auto_splits(users, nkv, bs, max_context_len)
+def decode_auto_splits(users: int, nkv: int, hd: int, max_context_len: int) -> int:
+    return _lib.lib().b200attn_decode_auto_splits(users, nkv, hd, max_context_len)
 
 
 def decode_workspace_bytes(users: int, nq: int, hd: int, splits: int) -> int:
@@ -239,7 +239,7 @@ def paged_decode(
     L = _lib.lib()
     if num_splits == 0:
         ctx = max_context_len if max_context_len > 0 else page_table.shape[1] * bs
-        num_splits = L.b200attn_decode_auto_splits(users, nkv, bs, ctx)
+        num_splits = L.b200attn_decode_auto_splits(users, nkv, hd, ctx)
     need = L.b200attn_decode_workspace_bytes(users, nq, hd, num_splits)
     ws = workspace if workspace is not None else _workspace(query.device, need)
     _lib.check(

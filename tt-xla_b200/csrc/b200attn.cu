@@ -271,24 +271,48 @@ int b200attn_kv_scatter_slots(void* k_cache, void* v_cache, const void* k_new, c
 }
 
 // -------------------------------------------------------------------------------- decode
-int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int block_size,
+int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
                                 int max_context_len) {
-  (void)block_size;
   if (num_users <= 0 || num_kv_heads <= 0 || max_context_len <= 0) return 1;
   int sm = 148;
   DeviceInfo* dev;
   if (get_device(&dev) == B200ATTN_OK) sm = dev->sm_count;
-  const int64_t slots = static_cast<int64_t>(sm) * 2;  // two CTAs per SM
+  // Cost model fitted to measurements on B200 (times in microseconds):
+  //   a CTA needs ~3 us to start streaming; alone on its SM it pulls one 64-token K+V tile
+  //   (32 KiB at head_size 128) in ~0.82 us; with `occ` CTAs per SM every CTA gets its share
+  //   of the SM's slice of ~7.2 TB/s; splitting costs a second launch (the combine) and the
+  //   fp32 partial round trip, ~16 us when the kernel is latency-bound.
+  const double tile_bytes = 2.0 * kDecTile * head_size * 2.0;
+  const double bw_per_sm = 7.2e6 / sm;                       // bytes per us
+  const int occ = head_size > 64 ? 2 : 3;                    // resident CTAs per SM
+  const double t_alone = 0.82 * tile_bytes / 32768.0;
   const int64_t tiles = (max_context_len + kDecTile - 1) / kDecTile;
-  const int64_t total_tiles = tiles * num_users * num_kv_heads;
-  // Chunks small enough that ~16 of them pass through every CTA slot (short tail, balanced
-  // ragged batches) but never below 4 tiles (pipeline fill and combine cost).
-  int64_t chunk = total_tiles / (slots * 16);
-  if (chunk < 4) chunk = 4;
-  int64_t splits = (tiles + chunk - 1) / chunk;
-  if (splits < 1) splits = 1;
-  if (splits > 128) splits = 128;
-  return static_cast<int>(splits);
+  const int64_t base = static_cast<int64_t>(num_users) * num_kv_heads;
+  const int64_t slots = static_cast<int64_t>(occ) * sm;
+  const int max_s = static_cast<int>(tiles < 128 ? tiles : 128);
+  int best_s = 1;
+  double best_t = 0.0;
+  for (int s = 1; s <= max_s; ++s) {
+    const int64_t chunk = (tiles + s - 1) / s;
+    const int64_t ctas = base * s;
+    double t;
+    if (ctas <= slots) {
+      const int64_t per_sm = (ctas + sm - 1) / sm;
+      const double t_tile = per_sm <= 1 ? t_alone
+                                        : (per_sm * tile_bytes / bw_per_sm > t_alone
+                                               ? per_sm * tile_bytes / bw_per_sm : t_alone);
+      t = 3.0 + chunk * t_tile;
+    } else {
+      const double cta = 3.0 + chunk * (occ * tile_bytes / bw_per_sm);
+      t = ctas * cta / slots + 0.5 * cta;    // work-conserving waves + half a CTA as tail (ragged batches)
+    }
+    if (s > 1) t += 16.0;
+    if (s == 1 || t < best_t * 0.99) {
+      best_t = t;
+      best_s = s;
+    }
+  }
+  return best_s;
 }
 
 size_t b200attn_decode_workspace_bytes(int num_users, int num_q_heads, int head_size,
@@ -328,7 +352,7 @@ int b200attn_paged_decode(void* out, int64_t out_row_stride, const void* q, int6
 
   if (max_context_len <= 0) max_context_len = page_table_width * block_size;
   if (num_splits == 0)
-    num_splits = b200attn_decode_auto_splits(num_users, num_kv_heads, block_size, max_context_len);
+    num_splits = b200attn_decode_auto_splits(num_users, num_kv_heads, head_size, max_context_len);
   const size_t need = b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits);
   if (num_splits > 1 && (!workspace || workspace_bytes < need || !aligned16(workspace)))
     return B200ATTN_ERR_WORKSPACE;
@@ -467,7 +491,7 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* 
       return B200ATTN_ERR_TOO_LARGE;
   } else {
     int ctx = max_context_len > 0 ? max_context_len : page_table_width * block_size;
-    num_splits = b200attn_decode_auto_splits(num_users, num_kv_heads, block_size, ctx);
+    num_splits = b200attn_decode_auto_splits(num_users, num_kv_heads, head_size, ctx);
     while (num_splits > 1 &&
            b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits) >
                B200ATTN_STATIC_WORKSPACE_BYTES)
