@@ -377,6 +377,55 @@ def run_prefill_bench(args, rank, world, device, peaks):
                          "peak_source": peaks["source"]}}
 
 
+def run_chunk_bench(args, rank, world, device, peaks):
+    """The prefill half of config 3: 2 chunks of 512 tokens appended to contexts of 4096 already in
+    the paged cache (nq 32 / nkv 8 / hd 128, block 64), heads sharded over the ranks.  One step =
+    paged_fill_cache of the chunk + chunked prefill attention over prefix + chunk."""
+    from b200attn import ops
+
+    users, T, start, nq, nkv, hd, bs = 2, 512, 4096, 32 // world, 8 // world, 128, 64
+    if nkv == 0:
+        return None
+    g = torch.Generator(device=device).manual_seed(11 + rank)
+    q = torch.randn(users * T, nq, hd, generator=g, device=device).bfloat16()
+    k = torch.randn(users, T, nkv, hd, generator=g, device=device).bfloat16()
+    v = torch.randn(users, T, nkv, hd, generator=g, device=device).bfloat16()
+    nblk = (start + T) // bs
+    nb = users * nblk + 1
+    pt = (torch.randperm(nb - 1)[: users * nblk] + 1).reshape(users, nblk).int().to(device)
+    fpt = torch.roll(pt, -(start // bs), dims=1).contiguous()
+    kc = torch.randn(nb, nkv, bs, hd, generator=g, device=device).bfloat16()
+    vc = torch.randn(nb, nkv, bs, hd, generator=g, device=device).bfloat16()
+    out = torch.empty_like(q)
+    cu_host = torch.arange(users + 1, dtype=torch.int32) * T
+    cu_dev = cu_host.to(device)
+    q_start = torch.full((users,), start, dtype=torch.int32, device=device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    times = []
+    for i in range(3 + 10):
+        flush.zero_()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        ops.paged_fill_cache(kc, vc, k, v, fpt)
+        ops.prefill(q, kc, vc, cu_host, scale=hd ** -0.5, page_table=pt, q_start=q_start,
+                    out=out, cu_q=cu_dev)
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    ms = max_over_ranks(statistics.mean(times), world, device)
+    flops = 4 * hd * 32 * users * (T * start + T * (T + 1) // 2)
+    tflops = flops / (ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"] * world
+    return {"workload": "c3_chunks_2x512_on_prefix_4096", "tflops": round(tflops, 1),
+            "ms": round(ms, 4), "flops": flops, "l2": "flushed between iterations",
+            "note": "2 sequences x 32 heads x 2 row blocks = 128 work items for 148 SMs",
+            "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": peak,
+                         "unit": "TFLOP/s", "frac": round(tflops / peak, 4),
+                         "peak_source": peaks["source"]}}
+
+
 # ------------------------------------------------------------------------------ config 5
 LLAMA31_8B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=4096,
                   intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
@@ -604,6 +653,7 @@ def main():
 
     r = run_decode_bench(args, wl, rank, world, device)
     prefill = None if args.no_prefill else run_prefill_bench(args, rank, world, device, peaks)
+    chunks = run_chunk_bench(args, rank, world, device, peaks) if args.workload == "c3" else None
     w = r["w"]
     del r["w"]
     cpu = None
@@ -646,6 +696,8 @@ def main():
         }
         if prefill:
             line["prefill"] = prefill
+        if chunks:
+            line["prefill_chunks"] = chunks
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
