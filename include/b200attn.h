@@ -119,6 +119,27 @@ int b200attn_kv_scatter_slots(void* k_cache, void* v_cache,
                               int block_size, int64_t num_blocks, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Rotary embedding fused with the slot-mapping KV-cache write (the caller on the left of the
+ * cache write).
+ * Replaces: TTRotaryEmbedding.forward(positions, query, key)
+ *           (integrations/vllm_plugin/vllm_tt/layers/rotary_embedding.py:51-66, NeoX style via
+ *           ApplyRotaryEmb.forward_static) followed by the KV-cache write above.
+ * cos / sin are computed on the fly from positions and inv_freq in fp32 and rounded to bf16, and
+ * every multiply / add of the rotation is rounded to bf16, as the reference layer computes them.
+ * q and k ([num_tokens, heads*head_size] rows with the given strides) are rotated in place; the
+ * rotated k and v go to slot_mapping[t] of the caches (negative slot: rotate only;
+ * slot_mapping == NULL: no cache write at all).  The first rotary_dim elements of each head are
+ * rotated (rotary_dim a multiple of 16, <= head_size); only is_neox_style = 1 is supported.
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_rope_kv_scatter_slots(void* q, int64_t q_stride, void* k, int64_t k_stride,
+                                   const void* v, int64_t v_stride, const int64_t* positions,
+                                   const float* inv_freq, int rotary_dim, int is_neox_style,
+                                   void* k_cache, void* v_cache, const int64_t* slot_mapping,
+                                   int num_tokens, int num_q_heads, int num_kv_heads,
+                                   int head_size, int block_size, int64_t num_blocks,
+                                   void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Paged GQA decode attention (one query token per user), split-KV + combine.
  * Replaces: torch.ops.tt.paged_scaled_dot_product_attention_decode with is_causal=True and
  *           cur_pos_tensor (custom_ops.py:1198-1331; call site attention.py:634-668).

@@ -155,3 +155,22 @@ def ref_chunked_sdpa(query, k_cache, v_cache, page_table, chunk_start, scale):
         query, k_cache, v_cache, page_table,
         torch.tensor([chunk_start], dtype=torch.int32), scale=scale,
     )
+
+
+def ref_rotary(positions, query, key, head_size, rotary_dim, base=500000.0, max_position=8192):
+    """The reference rotary layer (vllm_tt/layers/rotary_embedding.py) wrapped around vLLM's
+    RotaryEmbedding, on CPU.  Returns (rotated query, rotated key, inv_freq)."""
+    from vllm.config import DeviceConfig, VllmConfig, set_current_vllm_config
+    from vllm.model_executor.layers.rotary_embedding.base import RotaryEmbedding
+
+    path = os.path.join(REFERENCE_ROOT, "integrations", "vllm_plugin", "vllm_tt", "layers",
+                        "rotary_embedding.py")
+    mod = _state.get("rotary") or _load("vllm_tt_layers_rotary_embedding", path)
+    _state["rotary"] = mod
+    with set_current_vllm_config(VllmConfig(device_config=DeviceConfig(device="cpu"))):
+        layer = RotaryEmbedding(head_size=head_size, rotary_dim=rotary_dim,
+                                max_position_embeddings=max_position, base=base,
+                                is_neox_style=True, dtype=query.dtype)
+    tt = mod.TTRotaryEmbedding(layer)
+    q, k = tt(positions, query, key)
+    return q, k, tt.inv_freq.clone()

@@ -159,6 +159,37 @@ def chunked_sdpa(
     return torch.matmul(attn, gv)
 
 
+def rotary_embedding(
+    positions: torch.Tensor,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    inv_freq: torch.Tensor,
+    head_size: int,
+    rotary_dim: int,
+):
+    """integrations/vllm_plugin/vllm_tt/layers/rotary_embedding.py:51-66 with the NeoX-style
+    rotation of vLLM's ApplyRotaryEmb.forward_static: cos / sin from fp32 `positions x inv_freq`,
+    cast to the query dtype, then `o1 = x1*cos - x2*sin`, `o2 = x2*cos + x1*sin` in that dtype.
+    query [tokens, nq*hd], key [tokens, nkv*hd]; returns the rotated pair."""
+    pos = positions.flatten().to(torch.float32)
+    n = pos.shape[0]
+    freqs = torch.outer(pos, inv_freq)
+    cos = freqs.cos().to(query.dtype).unsqueeze(-2)
+    sin = freqs.sin().to(query.dtype).unsqueeze(-2)
+
+    def rot(x):
+        shape = x.shape
+        x = x.view(n, -1, head_size)
+        xr = x[..., :rotary_dim]
+        x1, x2 = torch.chunk(xr, 2, dim=-1)
+        o = torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1)
+        if rotary_dim != head_size:
+            o = torch.cat((o, x[..., rotary_dim:]), dim=-1)
+        return o.reshape(shape)
+
+    return rot(query), rot(key)
+
+
 # ------------------------------------------------------------------------------------------
 # The plugin's forward (attention.py:273-336) restated on top of the ops above, for batches in
 # the plugin's [users x tokens] form.  Returns (output, new_k_cache, new_v_cache).

@@ -199,6 +199,19 @@ def case_impl_forward():
                                      out_bf16=out, out_k=kv[0], out_v=kv[1], nq=nq, nkv=nkv))
 
 
+def case_rotary():
+    for name, (hd, rot) in {"rotary_hd64": (64, 64), "rotary_hd128": (128, 128),
+                            "rotary_hd64_partial32": (64, 32)}.items():
+        g = gen(70 + hd + rot)
+        tokens, nq, nkv = 6, 4, 2
+        pos = torch.tensor([0, 1, 17, 1023, 4096, 8191], dtype=torch.int64)
+        q = randn_bf16((tokens, nq * hd), g)
+        k = randn_bf16((tokens, nkv * hd), g)
+        qo, ko, inv_freq = ref.ref_rotary(pos, q, k, hd, rot)
+        save_case(name, dict(positions=pos, q=q, k=k, inv_freq=inv_freq, head_size=hd,
+                             rotary_dim=rot, out_q=qo, out_k=ko))
+
+
 if __name__ == "__main__":
     if not ref.available():
         sys.exit("reference tree not mounted; nothing generated")
@@ -208,6 +221,7 @@ if __name__ == "__main__":
     case_sdpa()
     case_chunked()
     case_impl_forward()
+    case_rotary()
     total = sum(os.path.getsize(os.path.join(os.path.dirname(__file__), f))
                 for f in os.listdir(os.path.dirname(__file__)) if f.endswith(".npz"))
     print(f"golden vectors written, {total / 1024:.0f} KiB")

@@ -103,3 +103,11 @@ def test_impl_chunk_matches_reference_forward():
     )
     assert torch.equal(k2, c["out_k"]) and torch.equal(v2, c["out_v"])
     assert (out - c["out_bf16"].float()).abs().max() <= 2e-2
+
+
+@pytest.mark.parametrize("name", ["rotary_hd64", "rotary_hd128", "rotary_hd64_partial32"])
+def test_rotary_matches_reference(name):
+    c = load_case(name)
+    q, k = restate.rotary_embedding(c["positions"], c["q"], c["k"], c["inv_freq"],
+                                    int(c["head_size"]), int(c["rotary_dim"]))
+    assert torch.equal(q, c["out_q"]) and torch.equal(k, c["out_k"])

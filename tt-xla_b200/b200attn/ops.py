@@ -172,6 +172,63 @@ def kv_scatter_slots(
     )
 
 
+def rope_kv_scatter_slots(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: Optional[torch.Tensor],
+    positions: torch.Tensor,
+    inv_freq: torch.Tensor,
+    rotary_dim: int,
+    head_size: int,
+    k_cache: Optional[torch.Tensor] = None,
+    v_cache: Optional[torch.Tensor] = None,
+    slot_mapping: Optional[torch.Tensor] = None,
+    is_neox_style: bool = True,
+) -> None:
+    """Rotary embedding of `query` / `key` IN PLACE, computed like the plugin's rotary layer
+    (layers/rotary_embedding.py:51-66), fused with the slot-mapping cache write of the rotated
+    key and of `value`.  `query` [tokens, nq*hd], `key` / `value` [tokens, nkv*hd] (dense rows,
+    any row stride); `positions` int64 [tokens]; `inv_freq` fp32 [rotary_dim/2].  Without
+    `slot_mapping` only the rotation is done."""
+    _need_cuda(query, key, value, positions, inv_freq, k_cache, v_cache, slot_mapping)
+    tokens = positions.numel()
+    if query.dim() != 2 or key.dim() != 2 or query.shape[0] != tokens or key.shape[0] != tokens:
+        raise ValueError("query / key must be [tokens, heads*head_size] with one row per position")
+    if query.dtype != torch.bfloat16 or key.dtype != torch.bfloat16:
+        raise ValueError("query / key must be bfloat16")
+    if query.stride(1) != 1 or key.stride(1) != 1:
+        raise ValueError("query / key rows must be dense")
+    nq, nkv = query.shape[1] // head_size, key.shape[1] // head_size
+    if positions.dtype != torch.int64 or not positions.is_contiguous():
+        raise ValueError("positions must be a dense int64 tensor")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2 \
+            or not inv_freq.is_contiguous():
+        raise ValueError("inv_freq must be dense float32 [rotary_dim / 2]")
+    nb = bs = 0
+    if slot_mapping is not None:
+        nb, nkv_c, bs, hd_c = _check_cache(k_cache, v_cache)
+        if nkv_c != nkv or hd_c != head_size:
+            raise ValueError("cache geometry differs from key geometry")
+        if value is None or value.shape != key.shape or value.stride(1) != 1:
+            raise ValueError("value must match key")
+        if slot_mapping.dtype != torch.int64 or slot_mapping.numel() < tokens:
+            raise ValueError("slot_mapping must be int64 with one entry per token")
+    L = _lib.lib()
+    _lib.check(
+        "b200attn_rope_kv_scatter_slots",
+        L.b200attn_rope_kv_scatter_slots(
+            query.data_ptr(), query.stride(0), key.data_ptr(), key.stride(0),
+            value.data_ptr() if value is not None else None,
+            value.stride(0) if value is not None else 0,
+            positions.data_ptr(), inv_freq.data_ptr(), rotary_dim, 1 if is_neox_style else 0,
+            k_cache.data_ptr() if slot_mapping is not None else None,
+            v_cache.data_ptr() if slot_mapping is not None else None,
+            slot_mapping.data_ptr() if slot_mapping is not None else None,
+            tokens, nq, nkv, head_size, bs, nb, _stream(query),
+        ),
+    )
+
+
 def decode_auto_splits(users: int, nkv: int, hd: int, max_context_len: int) -> int:
     return _lib.lib().b200attn_decode_auto_splits(users, nkv, hd, max_context_len)
 

@@ -10,6 +10,7 @@
 #include "decode.cuh"
 #include "kv_scatter.cuh"
 #include "prefill.cuh"
+#include "rope_scatter.cuh"
 
 namespace b200attn {
 
@@ -268,6 +269,55 @@ int b200attn_kv_scatter_slots(void* k_cache, void* v_cache, const void* k_new, c
   p.slot_mapping = slot_mapping;
   p.num_tokens = num_tokens;
   return launch_scatter(kScatterSlots, p, head_size, stream);
+}
+
+int b200attn_rope_kv_scatter_slots(void* q, int64_t q_stride, void* k, int64_t k_stride,
+                                   const void* v, int64_t v_stride, const int64_t* positions,
+                                   const float* inv_freq, int rotary_dim, int is_neox_style,
+                                   void* k_cache, void* v_cache, const int64_t* slot_mapping,
+                                   int num_tokens, int num_q_heads, int num_kv_heads,
+                                   int head_size, int block_size, int64_t num_blocks,
+                                   void* stream) {
+  if (!q || !k || !positions || !inv_freq) return B200ATTN_ERR_NULL_POINTER;
+  if (slot_mapping && (!v || !k_cache || !v_cache)) return B200ATTN_ERR_NULL_POINTER;
+  if (num_tokens < 0 || num_q_heads <= 0 || num_kv_heads <= 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (!is_neox_style) return B200ATTN_ERR_UNSUPPORTED;
+  if (head_size != 64 && head_size != 128) return B200ATTN_ERR_UNSUPPORTED;
+  if (rotary_dim <= 0 || rotary_dim > head_size || rotary_dim % 16 != 0)
+    return B200ATTN_ERR_UNSUPPORTED;
+  if (slot_mapping)
+    if (int rc = check_cache_geometry(num_kv_heads, head_size, block_size, num_blocks)) return rc;
+  if (!aligned16(q) || !aligned16(k) || (v && !aligned16(v)) || q_stride % 8 || k_stride % 8 ||
+      (v && v_stride % 8) || (k_cache && !aligned16(k_cache)) || (v_cache && !aligned16(v_cache)))
+    return B200ATTN_ERR_MISALIGNED;
+  if (q_stride < static_cast<int64_t>(num_q_heads) * head_size ||
+      k_stride < static_cast<int64_t>(num_kv_heads) * head_size)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (num_tokens == 0) return B200ATTN_OK;
+  RopeScatterParams p{};
+  p.q = static_cast<__nv_bfloat16*>(q);
+  p.q_stride = q_stride;
+  p.k = static_cast<__nv_bfloat16*>(k);
+  p.k_stride = k_stride;
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.v_stride = v_stride;
+  p.positions = positions;
+  p.inv_freq = inv_freq;
+  p.rotary_dim = rotary_dim;
+  p.k_cache = static_cast<uint4*>(k_cache);
+  p.v_cache = static_cast<uint4*>(v_cache);
+  p.slot_mapping = slot_mapping;
+  p.num_q_heads = num_q_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.head_size = head_size;
+  p.block_size = block_size;
+  p.num_blocks = num_blocks;
+  p.err_word = dev->err_word;
+  rope_kv_scatter_kernel<<<static_cast<unsigned>(num_tokens), 256, 0,
+                           static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // -------------------------------------------------------------------------------- decode
