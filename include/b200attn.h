@@ -119,6 +119,25 @@ int b200attn_kv_scatter_slots(void* k_cache, void* v_cache,
                               int block_size, int64_t num_blocks, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Step metadata built on the device (the producer on the left of every op above).
+ * Replaces: the host loop + host-to-device copies of TTModelRunner._prepare_inputs that fill
+ *           cache_position, page_table and fill_page_table
+ *           (integrations/vllm_plugin/vllm_tt/model_runner.py:1722-1741, 1945-1993).
+ * For row r < num_requests: cache_position = num_computed + num_scheduled - 1; page_table row =
+ * block_table row; fill_page_table row = that row rolled left by num_computed / block_size,
+ * first fill_page_table_width columns; slot_mapping[r, t] = block of position
+ * num_computed + t times block_size plus its offset, -1 for t >= num_scheduled.  Rows beyond
+ * num_requests, and rows with num_scheduled == 0, get cache_position -1 (resp. their true
+ * position), an all-zero page table (the null block) and slots of -1.
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_build_step_metadata(const int32_t* num_computed, const int32_t* num_scheduled,
+                                 const int32_t* block_table, int64_t block_table_stride,
+                                 int num_requests, int rows, int page_table_width,
+                                 int fill_page_table_width, int tokens_per_row, int block_size,
+                                 int32_t* cache_position, int32_t* page_table,
+                                 int32_t* fill_page_table, int64_t* slot_mapping, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Rotary embedding fused with the slot-mapping KV-cache write (the caller on the left of the
  * cache write).
  * Replaces: TTRotaryEmbedding.forward(positions, query, key)

@@ -27,6 +27,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int,
          c_int64, c_void_p],
     ),
+    "b200attn_build_step_metadata": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
     "b200attn_rope_kv_scatter_slots": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,

@@ -11,6 +11,7 @@
 #include "kv_scatter.cuh"
 #include "prefill.cuh"
 #include "rope_scatter.cuh"
+#include "step_metadata.cuh"
 
 namespace b200attn {
 
@@ -269,6 +270,31 @@ int b200attn_kv_scatter_slots(void* k_cache, void* v_cache, const void* k_new, c
   p.slot_mapping = slot_mapping;
   p.num_tokens = num_tokens;
   return launch_scatter(kScatterSlots, p, head_size, stream);
+}
+
+int b200attn_build_step_metadata(const int32_t* num_computed, const int32_t* num_scheduled,
+                                 const int32_t* block_table, int64_t block_table_stride,
+                                 int num_requests, int rows, int page_table_width,
+                                 int fill_page_table_width, int tokens_per_row, int block_size,
+                                 int32_t* cache_position, int32_t* page_table,
+                                 int32_t* fill_page_table, int64_t* slot_mapping, void* stream) {
+  if (!num_computed || !num_scheduled || !block_table || !cache_position || !page_table ||
+      !fill_page_table || !slot_mapping)
+    return B200ATTN_ERR_NULL_POINTER;
+  if (num_requests < 0 || rows < num_requests || page_table_width <= 0 ||
+      fill_page_table_width <= 0 || fill_page_table_width > page_table_width ||
+      tokens_per_row <= 0 || block_size <= 0)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (rows == 0) return B200ATTN_OK;
+  StepMetadataParams p{num_computed, num_scheduled, block_table, block_table_stride,
+                       num_requests, rows, page_table_width, fill_page_table_width,
+                       tokens_per_row, block_size, cache_position, page_table, fill_page_table,
+                       slot_mapping};
+  build_step_metadata_kernel<<<static_cast<unsigned>(rows), 128, 0,
+                               static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
 }
 
 int b200attn_rope_kv_scatter_slots(void* q, int64_t q_stride, void* k, int64_t k_stride,
