@@ -212,6 +212,25 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride,
                                  int block_size, int64_t num_blocks, float scale,
                                  int max_context_len, int num_splits, void* stream);
 
+/* b200attn_paged_decode with the two optional features of the reference op's signature
+ * (custom_ops.py:1198-1213: sliding_window_size, attention_sink):
+ *   sliding_window > 0: user u attends only keys j with cur_pos[u] - sliding_window < j <=
+ *                       cur_pos[u]; earlier pages are not read at all.
+ *   sinks != NULL:      fp32 [num_q_heads]; head h's softmax gets one more column with logit
+ *                       sinks[h] (in the scaled-score domain) that adds to the denominator only.
+ * The reference's CPU branch ignores both arguments (custom_ops.py:1256-1312), so their parity
+ * is checked against the published semantics, not against reference output. */
+int b200attn_paged_decode_ex(void* out, int64_t out_row_stride,
+                             const void* q, int64_t q_row_stride,
+                             const void* k_cache, const void* v_cache,
+                             const int32_t* page_table, int64_t page_table_stride,
+                             int page_table_width, const int32_t* cur_pos,
+                             int num_users, int num_q_heads, int num_kv_heads, int head_size,
+                             int block_size, int64_t num_blocks, float scale,
+                             int sliding_window, const float* sinks,
+                             int max_context_len, int num_splits,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Split count the library would pick for a decode batch (host cost model fitted to B200
  * measurements; no device access beyond the SM count).  max_context_len <= 0 means "unknown": the page-table width bounds it. */
 int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
@@ -248,6 +267,24 @@ int b200attn_prefill(void* out, int64_t out_row_stride,
                      int num_seqs, int total_q, int num_q_heads, int num_kv_heads,
                      int head_size, int block_size, int64_t num_blocks, float scale,
                      void* stream);
+
+/* b200attn_prefill with the reference op's optional sliding window
+ * (custom_ops.py:635-646 `sliding_window_size`): query row at absolute position p attends
+ * only keys j with p - sliding_window < j <= p (0 = full causal attention); KV tiles wholly
+ * below a query tile's window are neither loaded nor multiplied.  The reference's CPU branch
+ * ignores the argument (custom_ops.py:717-727), so this is checked against the published
+ * semantics, not against reference output. */
+int b200attn_prefill_ex(void* out, int64_t out_row_stride,
+                        const void* q, int64_t q_row_stride,
+                        const void* k_src, const void* v_src, int kv_is_paged,
+                        int64_t kv_token_stride,
+                        const int32_t* page_table, int64_t page_table_stride,
+                        int page_table_width,
+                        const int32_t* cu_q, const int32_t* cu_q_host,
+                        const int32_t* q_start,
+                        int num_seqs, int total_q, int num_q_heads, int num_kv_heads,
+                        int head_size, int block_size, int64_t num_blocks, float scale,
+                        int sliding_window, void* stream);
 
 /* Copies the device diagnostics word of the current device to *out_host (synchronises the
  * stream) and clears it.  0 = no kernel reported a problem since the last read. */

@@ -82,11 +82,19 @@ def paged_sdpa_decode(
     page_table: torch.Tensor,
     cur_pos: torch.Tensor,
     scale: Optional[float] = None,
+    sliding_window: Optional[int] = None,
+    sinks: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """custom_ops.py:1256-1312 with is_causal=True, for nq >= nkv (GQA: query head h reads KV
     head h // (nq/nkv), the `repeat_interleave` the reference intends at :1305-1306).
     query [1,users,nq,hd]; key/value caches [nb,nkv,bs,hd]; returns [1,users,nq,hd].
-    Rows with cur_pos < 0 yield NaN here exactly as in the reference (softmax of all -inf)."""
+    Rows with cur_pos < 0 yield NaN here exactly as in the reference (softmax of all -inf).
+
+    `sliding_window` and `sinks` are the op's `sliding_window_size` / `attention_sink`
+    arguments (custom_ops.py:1206-1207), which the reference's CPU branch accepts and ignores.
+    PARITY UNPINNED for these two: they follow the published definitions (a user at position p
+    attends keys p-W < j <= p; a sink is one extra softmax column per head whose weight is
+    dropped), not reference output."""
     _, users, nq, hd = query.shape
     nkv, bs = key.shape[1], key.shape[2]
     rep = nq // nkv
@@ -100,9 +108,15 @@ def paged_sdpa_decode(
         v = _gather_user_kv(value, page_table[u]).to(dt).repeat_interleave(rep, 0)
         mask = torch.zeros(max_seq, dtype=dt)
         mask[int(cur_pos[u]) + 1:] = float("-inf")
+        if sliding_window:
+            mask[: max(0, int(cur_pos[u]) + 1 - int(sliding_window))] = float("-inf")
         w = query[0, u].unsqueeze(1) @ k.transpose(-2, -1) * scale               # [nq,1,S]
         w = w + mask
-        w = torch.softmax(w, dim=-1)
+        if sinks is not None:
+            w = torch.cat([w, sinks.to(dt).view(nq, 1, 1)], dim=-1)
+            w = torch.softmax(w, dim=-1)[..., :-1]
+        else:
+            w = torch.softmax(w, dim=-1)
         out[u] = (w @ v).squeeze(1)
     return out.reshape(1, users, nq, hd)
 
@@ -113,9 +127,12 @@ def sdpa(
     value: torch.Tensor,
     is_causal: bool = True,
     scale: Optional[float] = None,
+    sliding_window: Optional[int] = None,
 ) -> torch.Tensor:
     """custom_ops.py:717-727: torch's scaled_dot_product_attention with enable_gqa, written out
-    as softmax(Q K^T * scale + causal mask) V.  query [B,nq,T,hd]; key/value [B,nkv,S,hd]."""
+    as softmax(Q K^T * scale + causal mask) V.  query [B,nq,T,hd]; key/value [B,nkv,S,hd].
+    `sliding_window` (the op's `sliding_window_size`, ignored by the reference's CPU branch;
+    PARITY UNPINNED) keeps keys i-W < j <= i for query row i."""
     B, nq, T, hd = query.shape
     nkv, S = key.shape[1], key.shape[2]
     rep = nq // nkv
@@ -125,6 +142,8 @@ def sdpa(
     w = query @ k.transpose(-2, -1) * scale
     if is_causal:
         keep = torch.ones(T, S, dtype=torch.bool).tril()
+        if sliding_window:
+            keep &= torch.ones(T, S, dtype=torch.bool).triu(1 - int(sliding_window))
         w = w.masked_fill(~keep, float("-inf"))
     w = torch.softmax(w, dim=-1)
     return w @ v
@@ -137,9 +156,12 @@ def chunked_sdpa(
     page_table: torch.Tensor,
     chunk_start: int,
     scale: Optional[float] = None,
+    sliding_window: Optional[int] = None,
 ) -> torch.Tensor:
     """custom_ops.py:1376-1433.  query [users,nq,T,hd] at absolute positions chunk_start+i;
-    key/value caches; page_table [users,nblk] (prefix + chunk).  Returns [users,nq,T,hd]."""
+    key/value caches; page_table [users,nblk] (prefix + chunk).  Returns [users,nq,T,hd].
+    `sliding_window`: as in `sdpa` (PARITY UNPINNED; the reference op has no such argument on
+    its CPU branch)."""
     users, nq, T, hd = query.shape
     nkv, bs = key.shape[1], key.shape[2]
     s_len = page_table.shape[1] * bs
@@ -154,7 +176,10 @@ def chunked_sdpa(
     attn = torch.matmul(query, gk.transpose(-2, -1)) * scale
     q_pos = chunk_start + torch.arange(T).view(T, 1)
     k_pos = torch.arange(s_len).view(1, s_len)
-    attn = attn.masked_fill(~(k_pos <= q_pos).view(1, 1, T, s_len), float("-inf"))
+    keep = k_pos <= q_pos
+    if sliding_window:
+        keep = keep & (k_pos > q_pos - int(sliding_window))
+    attn = attn.masked_fill(~keep.view(1, 1, T, s_len), float("-inf"))
     attn = torch.softmax(attn, dim=-1)
     return torch.matmul(attn, gv)
 
@@ -212,6 +237,8 @@ def impl_forward(
     batch_idx: Optional[torch.Tensor] = None,
     chunk_start_idx: Optional[torch.Tensor] = None,
     compute_dtype: Optional[torch.dtype] = None,
+    sliding_window: Optional[int] = None,
+    sinks: Optional[torch.Tensor] = None,
 ):
     q = query.reshape(num_users, -1, num_heads, head_size)
     k = key.reshape(num_users, -1, num_kv_heads, head_size)
@@ -223,20 +250,21 @@ def impl_forward(
         v_cache = paged_update_cache(v_cache, v.transpose(0, 1), cache_position, page_table)
         out = paged_sdpa_decode(
             q.transpose(0, 1).to(dt), k_cache.to(dt), v_cache.to(dt), page_table,
-            cache_position, scale,
+            cache_position, scale, sliding_window, sinks,
         ).transpose(0, 1)
     else:       # prefill (attention.py:485-511, 545-598)
+        assert sinks is None, "Attention sink is unsupported in SDPA prefill"  # attention.py:321
         fpt = fill_page_table if fill_page_table is not None else page_table
         k_cache = paged_fill_cache(k_cache, k.transpose(1, 2), fpt, batch_idx)
         v_cache = paged_fill_cache(v_cache, v.transpose(1, 2), fpt, batch_idx)
         if chunk_start_idx is not None:
             out = chunked_sdpa(
                 q.transpose(1, 2).to(dt), k_cache.to(dt), v_cache.to(dt), page_table,
-                int(chunk_start_idx.reshape(-1)[0]), scale,
+                int(chunk_start_idx.reshape(-1)[0]), scale, sliding_window,
             ).transpose(1, 2)
         else:
             out = sdpa(
                 q.transpose(1, 2).to(dt), k.transpose(1, 2).to(dt), v.transpose(1, 2).to(dt),
-                True, scale,
+                True, scale, sliding_window,
             ).transpose(1, 2)
     return out.reshape(-1, num_heads * head_size), k_cache, v_cache

@@ -44,12 +44,18 @@ def test_impl_constructor_errors():
         B200AttentionBackendImpl(8, 64, 0.125, 8, [1.0], None, "auto")
     with pytest.raises(NotImplementedError, match="encoder or decoder"):
         B200AttentionBackendImpl(8, 64, 0.125, 8, None, None, "auto", attn_type="encoder_decoder")
-    for kw in (dict(sliding_window=128), dict(kv_cache_dtype="fp8"), dict(logits_soft_cap=30.0)):
+    for kw in (dict(kv_cache_dtype="fp8"), dict(logits_soft_cap=30.0)):
         args = dict(num_heads=8, head_size=64, scale=0.125, num_kv_heads=8, alibi_slopes=None,
                     sliding_window=None, kv_cache_dtype="auto")
         args.update(kw)
         with pytest.raises(NotImplementedError):
             B200AttentionBackendImpl(**args)
+    with pytest.raises(ValueError, match="sliding_window"):
+        B200AttentionBackendImpl(8, 64, 0.125, 8, None, 0, "auto")
+    with pytest.raises(AssertionError, match="Sinks must have the same number of heads"):
+        B200AttentionBackendImpl(8, 64, 0.125, 8, None, None, "auto", sinks=torch.zeros(4))
+    impl = B200AttentionBackendImpl(8, 64, 0.125, 8, None, 128, "auto", sinks=torch.zeros(8))
+    assert impl.sliding_window == 128 and impl.sinks is not None
 
 
 def test_normalize_shapes_and_messages():

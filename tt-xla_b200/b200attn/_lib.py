@@ -43,6 +43,12 @@ SIGNATURES = {
          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_int, c_void_p,
          c_size_t, c_void_p],
     ),
+    "b200attn_paged_decode_ex": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p, c_int,
+         c_int, c_void_p, c_size_t, c_void_p],
+    ),
     "b200attn_paged_decode_static": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int,
@@ -55,6 +61,12 @@ SIGNATURES = {
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p,
          c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
          c_int64, c_float, c_void_p],
+    ),
+    "b200attn_prefill_ex": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p,
+         c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_int64, c_float, c_int, c_void_p],
     ),
     "b200attn_read_error_word": (c_int, [ctypes.POINTER(c_int32), c_void_p]),
 }

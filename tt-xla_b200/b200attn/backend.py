@@ -330,13 +330,29 @@ class B200AttentionBackendImpl:
             raise NotImplementedError(
                 f"kv_cache_dtype {kv_cache_dtype!r} is not supported (bf16 cache only)"
             )
-        if sliding_window is not None:
-            raise NotImplementedError("sliding_window attention is not supported")
+        if sliding_window is not None and int(sliding_window) <= 0:
+            raise ValueError(f"sliding_window must be positive, got {sliding_window}")
+        self._window = 0 if sliding_window is None else int(sliding_window)
         if logits_soft_cap is not None:
             raise NotImplementedError("logits_soft_cap is not supported")
         self.sinks = sinks
+        self._sinks_f32 = None   # ((device, data_ptr, version), fp32 copy)
         if self.sinks is not None:
-            raise NotImplementedError("attention sinks are not supported")
+            assert self.sinks.shape[0] == num_heads, (
+                "Sinks must have the same number of heads as the number of "
+                f"heads in the layer. Sinks shape: {sinks.shape}, num_heads: {num_heads}."
+            )   # attention.py:265-270
+
+    def _sinks_for(self, device) -> Optional[torch.Tensor]:
+        """fp32 copy of the per-head sink logits on `device` (made once; the decode kernel reads
+        fp32).  attention.py:650 hands the op the parameter as it is."""
+        if self.sinks is None:
+            return None
+        key = (str(device), self.sinks.data_ptr(), self.sinks._version)
+        if self._sinks_f32 is None or self._sinks_f32[0] != key:
+            copy = self.sinks.detach().to(device=device, dtype=torch.float32).contiguous()
+            self._sinks_f32 = (key, copy)
+        return self._sinks_f32[1]
 
     # ------------------------------------------------------------------ forward
     def forward(
@@ -481,6 +497,7 @@ class B200AttentionBackendImpl:
                 "only causal attention without an explicit mask is supported (the generative "
                 "path; model_runner.py:2004-2016)"
             )
+        assert self.sinks is None, "Attention sink is unsupported in SDPA prefill"  # :321
         users, tokens = inputs.users, inputs.query_num_tokens
         q = inputs.query.reshape(users * tokens, self.num_heads, self.head_size)
         out = output.reshape(users * tokens, self.num_heads, self.head_size)
@@ -492,7 +509,7 @@ class B200AttentionBackendImpl:
             ops.prefill(
                 q, kv_pair[0], kv_pair[1], cu_host, scale=self.scale,
                 page_table=attn_metadata.page_table, q_start=q_start.contiguous(), out=out,
-                cu_q=cu_dev,
+                cu_q=cu_dev, sliding_window=self._window,
             )
         elif shared_kv_mode:
             # Shared-KV layers read the target layer's cache (attention.py:562-574); the kernel
@@ -500,11 +517,13 @@ class B200AttentionBackendImpl:
             ops.prefill(
                 q, kv_pair[0], kv_pair[1], cu_host, scale=self.scale,
                 page_table=attn_metadata.page_table, q_start=None, out=out, cu_q=cu_dev,
+                sliding_window=self._window,
             )
         else:
             k = inputs.key.reshape(users * tokens, self.num_kv_heads, self.head_size)
             v = inputs.value.reshape(users * tokens, self.num_kv_heads, self.head_size)
-            ops.prefill(q, k, v, cu_host, scale=self.scale, out=out, cu_q=cu_dev)
+            ops.prefill(q, k, v, cu_host, scale=self.scale, out=out, cu_q=cu_dev,
+                        sliding_window=self._window)
 
     def _compute_decode_attention(self, inputs, kv_pair, attn_metadata: B200Metadata, output) -> None:
         """attention.py:634-668."""
@@ -517,6 +536,7 @@ class B200AttentionBackendImpl:
             scale=self.scale,
             out=output.reshape(users, self.num_heads, self.head_size),
             max_context_len=attn_metadata.max_seq_len,
+            sliding_window=self._window, sinks=self._sinks_for(output.device),
         )
 
     # ------------------------------------------------------------------ vLLM varlen form
@@ -539,12 +559,14 @@ class B200AttentionBackendImpl:
             ops.paged_decode(
                 q[:nd], kv_pair[0], kv_pair[1], md.block_table[:nd], md.decode_cur_pos,
                 scale=self.scale, out=out[:nd], max_context_len=md.max_seq_len,
+                sliding_window=self._window, sinks=self._sinks_for(output.device),
             )
         if md.prefill_cu_q_cpu is not None:
+            assert self.sinks is None, "Attention sink is unsupported in SDPA prefill"
             ops.prefill(
                 q[nd:], kv_pair[0], kv_pair[1], md.prefill_cu_q_cpu, scale=self.scale,
                 page_table=md.block_table[nd:], q_start=md.prefill_q_start, out=out[nd:],
-                cu_q=md.prefill_cu_q,
+                cu_q=md.prefill_cu_q, sliding_window=self._window,
             )
 
 

@@ -261,10 +261,15 @@ def paged_decode(
     num_splits: int = 0,
     max_context_len: int = 0,
     workspace: Optional[torch.Tensor] = None,
+    sliding_window: int = 0,
+    sinks: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Paged GQA decode attention: `tt.paged_scaled_dot_product_attention_decode` with
     is_causal=True and cur_pos_tensor (custom_ops.py:1198-1331).  `query`: [users, nq, hd]
-    (or the reference's [1, users, nq, hd]); returns / fills `out` of the same shape."""
+    (or the reference's [1, users, nq, hd]); returns / fills `out` of the same shape.
+    `sliding_window` > 0 limits each user to its last `sliding_window` keys; `sinks` (fp32
+    [nq]) adds one denominator-only softmax column per head (the op's `sliding_window_size` /
+    `attention_sink` arguments, which the reference CPU branch ignores)."""
     _need_cuda(query, k_cache, v_cache, page_table, cur_pos, out)
     nb, nkv, bs, hd = _check_cache(k_cache, v_cache)
     orig_shape = query.shape
@@ -294,17 +299,24 @@ def paged_decode(
     if scale is None:
         scale = hd ** -0.5
     L = _lib.lib()
+    if sinks is not None:
+        _need_cuda(sinks)
+        if sinks.dtype != torch.float32 or sinks.numel() != nq or not sinks.is_contiguous():
+            raise ValueError("sinks must be a dense float32 tensor with one entry per q head")
     if num_splits == 0:
         ctx = max_context_len if max_context_len > 0 else page_table.shape[1] * bs
+        if sliding_window > 0:
+            ctx = min(ctx, sliding_window + 64)
         num_splits = L.b200attn_decode_auto_splits(users, nkv, hd, ctx)
     need = L.b200attn_decode_workspace_bytes(users, nq, hd, num_splits)
     ws = workspace if workspace is not None else _workspace(query.device, need)
     _lib.check(
-        "b200attn_paged_decode",
-        L.b200attn_paged_decode(
+        "b200attn_paged_decode_ex",
+        L.b200attn_paged_decode_ex(
             out_t.data_ptr(), ostride, q.data_ptr(), qstride, k_cache.data_ptr(),
             v_cache.data_ptr(), page_table.data_ptr(), page_table.stride(0), page_table.shape[1],
-            cur_pos.data_ptr(), users, nq, nkv, hd, bs, nb, float(scale), max_context_len,
+            cur_pos.data_ptr(), users, nq, nkv, hd, bs, nb, float(scale), int(sliding_window),
+            sinks.data_ptr() if sinks is not None else None, max_context_len,
             num_splits, ws.data_ptr() if ws is not None else None,
             ws.numel() * ws.element_size() if ws is not None else 0, _stream(query),
         ),
@@ -324,6 +336,7 @@ def prefill(
     q_start: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
     cu_q: Optional[torch.Tensor] = None,
+    sliding_window: int = 0,
 ) -> torch.Tensor:
     """Causal varlen prefill (`tt.scaled_dot_product_attention`, custom_ops.py:635-742) when
     `page_table` is None and `k_src`/`v_src` are the fresh [tokens, nkv, hd] K/V of the same
@@ -385,15 +398,16 @@ def prefill(
         scale = hd ** -0.5
     L = _lib.lib()
     _lib.check(
-        "b200attn_prefill",
-        L.b200attn_prefill(
+        "b200attn_prefill_ex",
+        L.b200attn_prefill_ex(
             out_t.data_ptr(), ostride, q.data_ptr(), qstride, k.data_ptr(), v.data_ptr(),
             1 if paged else 0, kstride,
             page_table.data_ptr() if paged else None,
             page_table.stride(0) if paged else 0, page_table.shape[1] if paged else 0,
             cu_q.data_ptr(), cu_q_host.data_ptr(),
             q_start.data_ptr() if q_start is not None else None,
-            num_seqs, total_q, nq, nkv, hd, bs, nb, float(scale), _stream(query),
+            num_seqs, total_q, nq, nkv, hd, bs, nb, float(scale), int(sliding_window),
+            _stream(query),
         ),
     )
     return out if out is not None else out_t

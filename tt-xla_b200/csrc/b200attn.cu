@@ -172,11 +172,11 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   return static_cast<int>(e);
 }
 
-template <int HD, int BS>
-static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                          const PrefillParams& p, int sm_count, cudaStream_t s) {
+template <int HD, int BS, bool WIN>
+static int launch_prefill_win(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                              const PrefillParams& p, int sm_count, cudaStream_t s) {
   using L = PrefillSmem<HD>;
-  auto kern = prefill_tcgen05_kernel<HD, BS>;
+  auto kern = prefill_tcgen05_kernel<HD, BS, WIN>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -184,6 +184,15 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   dim3 grid(static_cast<unsigned>(p.total_items < sm_count ? p.total_items : sm_count));
   kern<<<grid, kPfThreads, L::kTotalBytes, s>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+// The sliding-window variant is a separate instantiation, so full causal attention carries none
+// of its masking or bookkeeping.
+template <int HD, int BS>
+static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const PrefillParams& p, int sm_count, cudaStream_t s) {
+  return p.window > 0 ? launch_prefill_win<HD, BS, true>(tq, tk, tv, p, sm_count, s)
+                      : launch_prefill_win<HD, BS, false>(tq, tk, tv, p, sm_count, s);
 }
 
 }  // namespace b200attn
@@ -407,6 +416,22 @@ int b200attn_paged_decode(void* out, int64_t out_row_stride, const void* q, int6
                           int num_users, int num_q_heads, int num_kv_heads, int head_size,
                           int block_size, int64_t num_blocks, float scale, int max_context_len,
                           int num_splits, void* workspace, size_t workspace_bytes, void* stream) {
+  return b200attn_paged_decode_ex(out, out_row_stride, q, q_row_stride, k_cache, v_cache,
+                                  page_table, page_table_stride, page_table_width, cur_pos,
+                                  num_users, num_q_heads, num_kv_heads, head_size, block_size,
+                                  num_blocks, scale, 0, nullptr, max_context_len, num_splits,
+                                  workspace, workspace_bytes, stream);
+}
+
+int b200attn_paged_decode_ex(void* out, int64_t out_row_stride, const void* q,
+                             int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                             const int32_t* page_table, int64_t page_table_stride,
+                             int page_table_width, const int32_t* cur_pos, int num_users,
+                             int num_q_heads, int num_kv_heads, int head_size, int block_size,
+                             int64_t num_blocks, float scale, int sliding_window,
+                             const float* sinks, int max_context_len, int num_splits,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  if (sliding_window < 0 || !(scale > 0.f)) return B200ATTN_ERR_BAD_ARGUMENT;
   if (!out || !q || !k_cache || !v_cache || !page_table || !cur_pos)
     return B200ATTN_ERR_NULL_POINTER;
   if (num_users < 0 || num_q_heads <= 0 || page_table_width <= 0 || num_splits < 0)
@@ -427,6 +452,8 @@ int b200attn_paged_decode(void* out, int64_t out_row_stride, const void* q, int6
   if (num_users > 65535 || num_kv_heads > 65535) return B200ATTN_ERR_TOO_LARGE;
 
   if (max_context_len <= 0) max_context_len = page_table_width * block_size;
+  if (sliding_window > 0 && max_context_len > sliding_window + kDecTile)
+    max_context_len = sliding_window + kDecTile;       // what a user streams at most
   if (num_splits == 0)
     num_splits = b200attn_decode_auto_splits(num_users, num_kv_heads, head_size, max_context_len);
   const size_t need = b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits);
@@ -453,6 +480,8 @@ int b200attn_paged_decode(void* out, int64_t out_row_stride, const void* q, int6
   p.num_splits = num_splits;
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = sliding_window;
+  p.sinks = sinks;
   p.err_word = dev->err_word;
   if (num_splits > 1) {
     const size_t rows_p = static_cast<size_t>(num_users) * num_q_heads * num_splits;
@@ -477,6 +506,21 @@ int b200attn_prefill(void* out, int64_t out_row_stride, const void* q, int64_t q
                      const int32_t* cu_q_host, const int32_t* q_start, int num_seqs, int total_q,
                      int num_q_heads, int num_kv_heads, int head_size, int block_size,
                      int64_t num_blocks, float scale, void* stream) {
+  return b200attn_prefill_ex(out, out_row_stride, q, q_row_stride, k_src, v_src, kv_is_paged,
+                             kv_token_stride, page_table, page_table_stride, page_table_width,
+                             cu_q, cu_q_host, q_start, num_seqs, total_q, num_q_heads,
+                             num_kv_heads, head_size, block_size, num_blocks, scale, 0, stream);
+}
+
+int b200attn_prefill_ex(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
+                        const void* k_src, const void* v_src, int kv_is_paged,
+                        int64_t kv_token_stride, const int32_t* page_table,
+                        int64_t page_table_stride, int page_table_width, const int32_t* cu_q,
+                        const int32_t* cu_q_host, const int32_t* q_start, int num_seqs,
+                        int total_q, int num_q_heads, int num_kv_heads, int head_size,
+                        int block_size, int64_t num_blocks, float scale, int sliding_window,
+                        void* stream) {
+  if (sliding_window < 0 || !(scale > 0.f)) return B200ATTN_ERR_BAD_ARGUMENT;
   if (!out || !q || !k_src || !v_src || !cu_q || !cu_q_host) return B200ATTN_ERR_NULL_POINTER;
   if (num_seqs < 0 || total_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0)
     return B200ATTN_ERR_BAD_ARGUMENT;
@@ -539,6 +583,7 @@ int b200attn_prefill(void* out, int64_t out_row_stride, const void* q, int64_t q
   p.num_kv_heads = num_kv_heads;
   p.group = num_q_heads / num_kv_heads;
   p.kv_is_paged = kv_is_paged ? 1 : 0;
+  p.window = sliding_window;
   p.total_items = total_tiles * num_q_heads;
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -36,8 +36,20 @@ struct DecodeParams {
   int num_splits;
   int64_t num_blocks;
   float scale_log2; // softmax scale * log2(e)
+  int window;       // sliding window size in keys (0 = attend to the whole context)
+  const float* sinks;  // [num_q_heads] attention-sink logits (scaled domain), or NULL
   int* err_word;
 };
+
+// Folds an attention sink into a row's (max, sum): the sink is one more softmax column that
+// contributes to the denominator only.  Returns the factor the accumulated values scale by.
+__device__ __forceinline__ float apply_sink(float& m, float& l, float sink_log2) {
+  const float m2 = fmaxf(m, sink_log2);
+  const float f = (m == -INFINITY) ? 0.f : fast_exp2(m - m2);
+  l = l * f + fast_exp2(sink_log2 - m2);
+  m = m2;
+  return f;
+}
 
 template <int HD, int BS, int STAGES>
 struct DecodeSmem {
@@ -73,9 +85,11 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int lane = threadIdx.x & 31;
 
   const int ctx = p.cur_pos[user] + 1;  // keys 0 .. cur_pos
+  const int lo = (p.window > 0 && ctx > p.window) ? ctx - p.window : 0;   // first key attended
   const int n_tiles = ctx > 0 ? (ctx + kDecTile - 1) / kDecTile : 0;
-  const int tiles_per_split = (n_tiles + p.num_splits - 1) / p.num_splits;
-  const int t_begin = split * tiles_per_split;
+  const int t_lo = lo / kDecTile;
+  const int tiles_per_split = (n_tiles - t_lo + p.num_splits - 1) / p.num_splits;
+  const int t_begin = t_lo + split * tiles_per_split;
   const int t_end = min(n_tiles, t_begin + tiles_per_split);
   const int G = p.group;
 
@@ -210,8 +224,8 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
     const uint32_t vbase = kbase + L::kTensorBytes;
     const int tok0 = t * kDecTile + warp * 16;   // first token of this warp's slice
 
-    if (tok0 < ctx) {
-      const bool tail = (tok0 + 16 > ctx);
+    if (tok0 < ctx && tok0 + 16 > lo) {       // at least one of this warp's keys is attended
+      const bool tail = (tok0 + 16 > ctx) || (tok0 < lo);
       if (tail) {
         // Zero this warp's V rows past the context so that stale or non-finite cache
         // contents cannot reach the accumulator through 0 * x.
@@ -255,7 +269,7 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int tok = tok0 + i * 8 + tq * 2 + (j & 1);
-            if (tok >= ctx) s[i][j] = -INFINITY;
+            if (tok >= ctx || tok < lo) s[i][j] = -INFINITY;
           }
       }
       float mx_lo = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -265,7 +279,7 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
       const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-      // tok0 < ctx guarantees at least one unmasked key, so mn_* is finite here.
+      // the guard above leaves at least one unmasked key, so mn_* is finite here.
       const float c_lo = fast_exp2(m_lo - mn_lo), c_hi = fast_exp2(m_hi - mn_hi);
       m_lo = mn_lo;
       m_hi = mn_hi;
@@ -352,6 +366,7 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
     }
     const int head = kvh * G + r;
     if (p.num_splits == 1) {
+      if (p.sinks) acc *= apply_sink(m, l, p.sinks[head] * 1.4426950408889634f);
       p.out[static_cast<int64_t>(user) * p.out_row_stride + head * HD + d] =
           __float2bfloat16(l > 0.f ? acc / l : 0.f);
     } else {
@@ -380,6 +395,7 @@ __global__ void __launch_bounds__(HD) decode_combine_kernel(const DecodeParams p
     acc += f * p.part_o[(row0 + s) * HD + d];
     l += f * ml.y;
   }
+  if (p.sinks) acc *= apply_sink(m, l, p.sinks[head] * 1.4426950408889634f);
   p.out[static_cast<int64_t>(user) * p.out_row_stride + head * HD + d] =
       __float2bfloat16(l > 0.f ? acc / l : 0.f);
 }

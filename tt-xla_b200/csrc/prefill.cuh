@@ -51,6 +51,7 @@ struct PrefillParams {
   int num_kv_heads;
   int group;
   int kv_is_paged;
+  int window;          // sliding window size in keys (0 = full causal attention)
   int total_items;     // (256-row blocks over all sequences) x num_q_heads
   int64_t num_blocks;
   float scale_log2;
@@ -86,8 +87,11 @@ struct PrefillItemKey {
 // What every role needs to know about one work item.
 struct PrefillItem {
   int seq, head, q0, seq_q_begin, seq_len_q, start;
-  int rows_valid[kPfQTiles], first_pos[kPfQTiles], n_tiles[kPfQTiles];
-  int n_max;
+  int rows_valid[kPfQTiles], first_pos[kPfQTiles];
+  // KV tiles are counted relative to the item's first tile j0 (0 without a sliding window):
+  // query tile w works on relative tiles skip[w] .. n_rel[w]-1.
+  int j0, skip[kPfQTiles], n_rel[kPfQTiles];
+  int n_max;          // relative tiles of the item (the larger n_rel)
 };
 
 // Item index -> (sequence, 256-row block, head).  `cu` is cu_q (shared-memory copy when the
@@ -147,7 +151,8 @@ __device__ __forceinline__ PrefillItemKey prefill_find_item(const PrefillParams&
   return key;
 }
 
-__device__ __forceinline__ bool prefill_expand_item(const PrefillItemKey& key, const int32_t* cu,
+__device__ __forceinline__ bool prefill_expand_item(const PrefillParams& p,
+                                                    const PrefillItemKey& key, const int32_t* cu,
                                                     PrefillItem& it) {
   if (key.seq < 0) return false;
   it.seq = key.seq;
@@ -160,10 +165,20 @@ __device__ __forceinline__ bool prefill_expand_item(const PrefillItemKey& key, c
   for (int w = 0; w < kPfQTiles; ++w) {
     it.rows_valid[w] = max(0, min(kPfM, it.seq_len_q - it.q0 - w * kPfM));
     it.first_pos[w] = it.start + it.q0 + w * kPfM;
-    it.n_tiles[w] =
-        it.rows_valid[w] > 0 ? (it.first_pos[w] + it.rows_valid[w] - 1) / kPfN + 1 : 0;
   }
-  it.n_max = max(it.n_tiles[0], it.n_tiles[1]);   // tile A never needs more KV tiles than B
+  // first key any row of tile A may attend (tile A starts lowest)
+  const int lo = (p.window > 0 && it.first_pos[0] + 1 > p.window) ? it.first_pos[0] + 1 - p.window : 0;
+  it.j0 = lo / kPfN;
+#pragma unroll
+  for (int w = 0; w < kPfQTiles; ++w) {
+    const int n_abs =
+        it.rows_valid[w] > 0 ? (it.first_pos[w] + it.rows_valid[w] - 1) / kPfN + 1 : 0;
+    const int lo_w =
+        (p.window > 0 && it.first_pos[w] + 1 > p.window) ? it.first_pos[w] + 1 - p.window : 0;
+    it.n_rel[w] = n_abs > 0 ? n_abs - it.j0 : 0;
+    it.skip[w] = n_abs > 0 ? lo_w / kPfN - it.j0 : 0;
+  }
+  it.n_max = max(it.n_rel[0], it.n_rel[1]);   // tile A never ends later than tile B
   return true;
 }
 
@@ -172,7 +187,7 @@ __device__ __forceinline__ int prefill_item_of(int round, int cta, int num_ctas)
   return round * num_ctas + ((round & 1) ? (num_ctas - 1 - cta) : cta);
 }
 
-template <int HD, int BS>
+template <int HD, int BS, bool WIN>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                        const __grid_constant__ CUtensorMap tm_k,
@@ -218,7 +233,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     const PrefillItemKey key =
         round < kPfItemTable ? item_table[round]
                              : prefill_find_item(p, cu, prefill_item_of(round, blockIdx.x, gridDim.x));
-    return prefill_expand_item(key, cu, it);
+    return prefill_expand_item(p, key, cu, it);
   };
 
   if (threadIdx.x == 0) {
@@ -277,7 +292,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int last_pos = it.start + min(it.seq_len_q, it.q0 + kPfRowsPerItem) - 1;
       const int n_pages = last_pos / BS + 1;      // pages holding keys 0 .. last_pos
       for (int i = 0; i < 2 * it.n_max; ++i, ++ring_i) {
-        const int j = i >> 1;
+        const int j = (WIN ? it.j0 : 0) + (i >> 1);          // absolute KV tile
         const bool is_v = i & 1;
         const int slot = ring_i % kSlots;
         mbar_wait(&empty[slot], ((ring_i / kSlots) & 1) ^ 1, abort_flag, p.err_word);
@@ -351,9 +366,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         umma_commit(&s_full[w]);
       }
     };
-    auto issue_pv = [&](int w, int j, uint32_t v_ring) {   // O_w (+)= P_w V_j
+    auto issue_pv = [&](int w, bool first, uint32_t v_ring) {   // O_w (+)= P_w V_j
       mbar_wait(&p_full[w], tiles_done[w] & 1, abort_flag, p.err_word);
-      if (j == 0)   // O_w of the previous item must have been read out before it is overwritten
+      if (first)    // O_w of the previous item must have been read out before it is overwritten
         mbar_wait(&o_empty[w], (items_done[w] & 1) ^ 1, abort_flag, p.err_word);
       tc_fence_after_sync();
       const uint32_t p_tmem = tmem_base + w * kPfN;   // P over the first 64 columns of S_w
@@ -364,7 +379,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int kk = 0; kk < kPfN / 16; ++kk) {
           // A: 16 keys = 8 packed 32-bit columns per step; B: 16 keys = 2048 B further on
           umma_ts(d, p_tmem + kk * 8, desc(v_lo + kk * (2048 >> 4)), idesc_pv,
-                  (j > 0) || (kk > 0));
+                  !first || (kk > 0));
         }
         umma_commit(&pv_done[w]);
       }
@@ -378,7 +393,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       wait_ring(ring_base);                         // K_0
 #pragma unroll
       for (int w = 0; w < kPfQTiles; ++w)
-        if (it.n_tiles[w] > 0) issue_qk(w, ring_base);
+        if (it.n_rel[w] > 0 && (!WIN || it.skip[w] == 0)) issue_qk(w, ring_base);
       release_ring(ring_base);
       if (it.n_max == 1 && leader) umma_commit(q_empty);
       for (int j = 0; j < it.n_max; ++j) {
@@ -387,15 +402,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         bool next_k_ready = false;
 #pragma unroll
         for (int w = 0; w < kPfQTiles; ++w) {
-          if (j < it.n_tiles[w]) {
-            issue_pv(w, j, ring_base + 2 * j + 1);
-            if (j + 1 < it.n_tiles[w]) {
-              if (!next_k_ready) {
-                wait_ring(ring_base + 2 * j + 2);   // K_{j+1}
-                next_k_ready = true;
-              }
-              issue_qk(w, ring_base + 2 * j + 2);
+          const int skip_w = WIN ? it.skip[w] : 0;
+          if (j >= skip_w && j < it.n_rel[w]) issue_pv(w, j == skip_w, ring_base + 2 * j + 1);
+          if (j + 1 >= skip_w && j + 1 < it.n_rel[w]) {
+            if (!next_k_ready) {
+              wait_ring(ring_base + 2 * j + 2);   // K_{j+1}
+              next_k_ready = true;
             }
+            issue_qk(w, ring_base + 2 * j + 2);
           }
         }
         release_ring(ring_base + 2 * j + 1);
@@ -407,7 +421,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
 #pragma unroll
       for (int w = 0; w < kPfQTiles; ++w)
-        if (it.n_tiles[w] > 0) ++items_done[w];
+        if (it.n_rel[w] > 0) ++items_done[w];
       ring_base += 2 * it.n_max;
     }
   } else {
@@ -422,11 +436,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
       if (!get_item(round, it)) continue;
-      const int my_tiles = it.n_tiles[w];
-      if (my_tiles == 0) continue;
+      if (it.n_rel[w] <= 0) continue;
       const int q_pos = it.first_pos[w] + row;
       float m_run = -INFINITY, l_run = 0.f;
-      for (int j = 0; j < my_tiles; ++j, ++tiles_done) {
+      const int skip_w = WIN ? it.skip[w] : 0;
+      for (int jr = skip_w; jr < it.n_rel[w]; ++jr, ++tiles_done) {
+        const int j = (WIN ? it.j0 : 0) + jr;    // absolute KV tile
+        const bool first = jr == skip_w;
         mbar_wait(&s_full[w], tiles_done & 1, abort_flag, p.err_word);
         tc_fence_after_sync();
         uint32_t sreg[4][32];
@@ -442,6 +458,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             for (int k = 0; k < 32; ++k)
               if (key0 + c * 32 + k > q_pos) sreg[c][k] = 0xff800000u;   // -inf
         }
+        if (WIN && key0 < it.first_pos[w] + kPfM - p.window) {   // below some row's window
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              if (key0 + c * 32 + k + p.window <= q_pos) sreg[c][k] = 0xff800000u;   // -inf
+        }
         // row max of the raw scores (scale > 0), four independent chains
         float mx[4];
 #pragma unroll
@@ -456,13 +479,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const float mx_s = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
         float m_new = m_run;
         if (mx_s - m_run > kPfRescaleThreshold) m_new = mx_s;   // also taken when m_run = -inf
-        const float corr = fast_exp2(m_run - m_new);
-        const bool rescale = (m_new != m_run) && (j > 0);
+        // a row whose keys are all masked so far (possible only under a sliding window) keeps
+        // m = -inf: its weights and its correction factor are 0, not exp2(-inf + inf)
+        const float corr = (WIN && m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+        const bool rescale = (m_new != m_run) && !first;
         m_run = m_new;
         // p = 2^(s*scale - m): packed FMA, then ex2; two packed running sums.  Each 32-key
         // chunk goes straight back to tensor memory as 16 packed bf16x2 columns.  QK_j has
         // retired (s_full), and PV_{j-1} was issued before it, so S_w / P_w / O_w are quiescent.
-        const uint64_t negm2 = pack_f32x2(-m_new, -m_new);
+        const float m_sub = (WIN && m_new == -INFINITY) ? 0.f : m_new;
+        const uint64_t negm2 = pack_f32x2(-m_sub, -m_sub);
         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -487,7 +513,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           l_run = l_run * corr + ((a0 + a1) + (b0 + b1));
         }
         // O row rescale (rare: only when the running max moved by more than the threshold).
-        if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+        if (!first && __any_sync(0xffffffffu, rescale)) {
           const float f = rescale ? corr : 1.f;
           const uint64_t f2 = pack_f32x2(f, f);
 #pragma unroll
