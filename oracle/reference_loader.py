@@ -174,3 +174,14 @@ def ref_rotary(positions, query, key, head_size, rotary_dim, base=500000.0, max_
     tt = mod.TTRotaryEmbedding(layer)
     q, k = tt(positions, query, key)
     return q, k, tt.inv_freq.clone()
+
+
+def load_swa_utils():
+    """The reference's sliding-window ring helpers (vllm_tt/swa_cache_utils.py: pure ints/numpy)."""
+    if "swa" not in _state:
+        if not available():
+            raise RuntimeError(f"reference tree not found under {REFERENCE_ROOT}")
+        path = os.path.join(REFERENCE_ROOT, "integrations", "vllm_plugin", "vllm_tt",
+                            "swa_cache_utils.py")
+        _state["swa"] = _load("vllm_tt_swa_cache_utils", path)
+    return _state["swa"]

@@ -243,3 +243,40 @@ def test_impl_forward_window_and_sinks(clean_error_word):
     with pytest.raises(AssertionError, match="unsupported in SDPA prefill"):
         impl_s.forward(None, case.q.cuda(), case.k.cuda(), case.v.cuda(), [kc, vc], md,
                        output=out)
+
+
+@pytest.mark.parametrize("hd,bs", [(64, 32), (128, 64)])
+def test_decode_on_ring_cache_equals_windowed_decode_on_full_cache(hd, bs, clean_error_word):
+    """The reference's sliding-window ring (swa_cache_utils.py, model_runner.py:1753-1815): each
+    request keeps only `window_blocks` physical blocks, the page table lists them rotated into
+    logical order and the position is counted from the first listed block.  Decoding on that
+    ring must give what windowed decode over the whole context gives."""
+    import numpy as np
+
+    from b200attn import ops, swa
+
+    window, users = 100, 6
+    case = make_decode_case(nq=8, nkv=2, hd=hd, bs=bs, users=users, ctx_lo=1, ctx_hi=900, seed=13)
+    want = _decode_oracle(case, window)
+    wb = swa.sliding_window_blocks(window, bs, 1 << 20)
+    slots = np.array([3, 0, 5, 1, 4, 2])
+    start, pos_rel = swa.ring_window_view(case.ctx_lens.numpy(), bs, wb)
+    ring_pt = swa.build_sliding_ring_page_table(start, slots, wb, wb)
+    g = torch.Generator().manual_seed(99)
+    nb_ring = swa.sliding_ring_phys_blocks(wb, users)
+    ring_k = randn_bf16((nb_ring, 2, bs, hd), g)      # stale contents everywhere else
+    ring_v = randn_bf16((nb_ring, 2, bs, hd), g)
+    for u in range(users):
+        cur_block = (int(case.ctx_lens[u]) - 1) // bs
+        for b in range(int(start[u]), cur_block + 1):
+            phys = 1 + int(slots[u]) * wb + b % wb
+            assert phys == ring_pt[u, b - int(start[u])]
+            ring_k[phys] = case.k_cache[int(case.page_table[u, b])]
+            ring_v[phys] = case.v_cache[int(case.page_table[u, b])]
+    out = ops.paged_decode(
+        case.q.reshape(users, 8, hd).cuda(), ring_k.cuda(), ring_v.cuda(),
+        torch.from_numpy(ring_pt.astype(np.int32)).cuda(),
+        torch.from_numpy(pos_rel.astype(np.int32)).cuda(), scale=case.scale,
+        sliding_window=window,
+    ).cpu()
+    assert_attention_close(out, want, "ring decode")
