@@ -434,6 +434,93 @@ LLAMA31_8B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden
                   tie_word_embeddings=False, hidden_act="silu", bos_token_id=1, eos_token_id=2)
 
 
+def run_rowlinear_bench(args):
+    """Row-parallel linear + all-reduce of the end-to-end model's decode step (config 5: 64 token
+    rows, hidden 4096, o_proj K = 4096 / TP and down_proj K = 14336 / TP): the fused launch of
+    this repository against torch's GEMM followed by an NCCL all-reduce, both walking a set of 32
+    different weight matrices (one per layer, larger than L2 together) as the model does.  Device
+    time by CUDA events, max over ranks."""
+    rank, world, local = dist_setup(args.gpus)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    sys.path.insert(0, os.path.join(ROOT, "tt-xla_b200"))
+    from b200attn import ops, tp_linear
+
+    comm = tp_linear.RowLinearComm(dist.group.WORLD, max_n=4096, max_tokens=128) if world > 1 else None
+    tokens, hidden, layers = 64, 4096, 32
+    peaks = load_peaks()
+    results = {}
+    for name, k_full in (("o_proj", 4096), ("down_proj", 14336)):
+        kl = k_full // world
+        g = torch.Generator(device=device).manual_seed(7 + rank)
+        ws = [(torch.randn(hidden, kl, generator=g, device=device) * 0.02).to(torch.bfloat16)
+              for _ in range(layers)]
+        x = torch.randn(tokens, kl, generator=g, device=device).to(torch.bfloat16)
+        out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device)
+
+        def fused():
+            for w in ws:
+                tp_linear.rowlinear_allreduce(x, w, comm, out=out)
+
+        def stock():
+            for w in ws:
+                torch.matmul(x, w.t(), out=out)
+                if world > 1:
+                    dist.all_reduce(out)
+
+        def timed(fn):
+            # one pass over the 32 layers captured as a CUDA graph (how the serving engine runs
+            # its decode steps), so that device time is measured and not Python launch time
+            fn()
+            barrier(world)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            for _ in range(args.warmup):
+                graph.replay()
+            barrier(world)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return max_over_ranks(e0.elapsed_time(e1) * 1e3 / (args.steps * layers), world, device)
+
+        us_stock = timed(stock)
+        us_fused = timed(fused)
+        wbytes = hidden * kl * 2
+        results[name] = {"k_local": kl, "fused_us": round(us_fused, 2), "stock_us": round(us_stock, 2),
+                         "weight_gbs_fused": round(wbytes / us_fused / 1e3, 1),
+                         "weight_gbs_stock": round(wbytes / us_stock / 1e3, 1)}
+    word = ops.read_error_word()
+    if comm is not None:
+        dist.barrier()
+        comm.close()
+    if rank == 0:
+        o = results["o_proj"]
+        print(json.dumps({
+            "metric": "rowlinear_allreduce_us", "value": o["fused_us"], "unit": "us", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(o["fused_us"] * 32e-3, 4),
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "c5_rowparallel_linear_allreduce_B64_hidden4096",
+                       "parallelism": f"tp{world}", "step": "32 layers back to back, replayed as one CUDA graph",
+                       "l2": "32 distinct weight matrices per pass (larger than L2 together)",
+                       "stock": "torch.matmul + NCCL all-reduce"},
+            "layers": results, "error_word": word,
+            "roofline": {"bound": "hbm", "achieved": o["weight_gbs_fused"], "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": round(o["weight_gbs_fused"] / peaks["hbm_gbs"], 4),
+                         "traffic": None, "peak_source": peaks["source"],
+                         "note": "weight bytes of one o_proj launch / its device time, all-reduce "
+                                 "included in the time"},
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_e2e_llama(args):
     """Config 5: end-to-end decode of a random-init Llama-3.1-8B through vLLM with this
     repository's backend registered as the CUSTOM attention backend (the way the reference
@@ -448,6 +535,8 @@ def run_e2e_llama(args):
     rank = int(os.environ.get("RANK", "0"))
     if world > 1:
         os.environ["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"
+    if args.fused_linear:
+        os.environ["B200ATTN_FUSED_ROW_PARALLEL"] = "1"
     from vllm import LLM, SamplingParams
 
     cfg_dir = tempfile.mkdtemp(prefix="llama31_8b_cfg_")
@@ -485,6 +574,10 @@ def run_e2e_llama(args):
     decode_s = t_full - t_first
     decode_tok = batch * (gen_len - 1)
     tok_s = decode_tok / decode_s
+    err_word = None
+    if world > 1:          # the engine runs in this process: its kernels' diagnostics word is ours
+        from b200attn import ops
+        err_word = ops.read_error_word()
     # stop the engine first so that its shutdown messages do not follow the result line
     try:
         llm.llm_engine.engine_core.shutdown()
@@ -506,10 +599,13 @@ def run_e2e_llama(args):
             "data": "synthetic",
             "config": {"workload": "c5_llama31_8b_e2e_decode_B64_P1024_G256",
                        "parallelism": f"tp{world}", "attention_backend": args.attn,
+                       "row_parallel_linear": "fused GEMM + all-reduce" if args.fused_linear
+                       else "vLLM GEMM + all-reduce",
                        "weights": "random init (vLLM dummy loader)",
                        "timing": "wall clock around LLM.generate; decode = (256-token run) - "
                                  "(1-token run); decode steps are CUDA-graph replays"},
             "ttft_s": round(t_first, 4), "generate_s": round(t_full, 4), "tokens": n_tok,
+            "error_word": err_word,
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                          "traffic": None, "peak_source": peaks["source"],
@@ -610,15 +706,25 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c5", "rowlinear"])
     ap.add_argument("--attn", default="b200", choices=["b200", "stock"],
                     help="c5 only: this repository's backend, or vLLM's stock one for comparison")
+    ap.add_argument("--fused-linear", action="store_true",
+                    help="c5 only: o_proj / down_proj through the fused GEMM + all-reduce launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="prefill: run only the config-2 prefill part (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.workload == "rowlinear":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "the row-parallel linear is a multi-GPU collective; the reference arm "
+                              "covers the decode-attention workloads"}))
+            return
+        run_rowlinear_bench(args)
+        return
     if args.workload == "c5":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable":

@@ -286,6 +286,53 @@ int b200attn_prefill_ex(void* out, int64_t out_row_stride,
                         int head_size, int block_size, int64_t num_blocks, float scale,
                         int sliding_window, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Row-parallel linear layer with the tensor-parallel all-reduce fused into its epilogue.
+ * Replaces: a row-sharded linear layer whose partial sums are all-reduced -- the reference marks
+ * the weight sharded along its input dimension and leaves the all-reduce to the compiler
+ * (vllm_tt/vllm_distributed_utils.py:356-363, partition_row_parallel_linear; it is the o_proj /
+ * down_proj collective of the end-to-end model), vLLM's RowParallelLinear.forward runs a GEMM and
+ * then tensor_model_parallel_all_reduce.  Here one launch per rank computes
+ *     out[t, n] = sum over ranks r of sum_k x_r[t, k] * w_r[n, k]       (bf16 partials, fp32 sum)
+ * for num_tokens <= 128: tcgen05 GEMM tiles (clusters split K) whose epilogue pushes the rank's
+ * bf16-rounded partial sums into every peer's staging area as 8-byte units that carry their own
+ * arrival flag (plain peer stores), waits (bounded) for the peers' units and adds all ranks'
+ * partials in rank order, so all ranks return identical bits (bf16 partials, fp32 sum: what
+ * vLLM's all-reduce of the GEMM outputs computes).
+ *
+ * Communicator: one device buffer per rank, b200attn_comm_bytes(world, max_tokens, max_n) bytes,
+ * zero-initialised, mapped into every rank's process.  b200attn_comm_alloc / _export / _import /
+ * _close / _free wrap cudaMalloc and the CUDA IPC handle calls so that a host without its own
+ * CUDA runtime binding can set it up: each rank allocates, exports 64 handle bytes, exchanges
+ * them over any channel, imports its peers' handles.  comm_bufs[r] is rank r's buffer as mapped
+ * in the calling process (own buffer at [rank]); with world == 1 it may be NULL and the call is
+ * a plain GEMM.
+ *
+ * All ranks must issue the same sequence of calls with the same shapes on one stream each.  The
+ * call is asynchronous and allocation-free.  A peer that does not arrive within peer_timeout_ns
+ * (0 = 10 s) makes the kernel give up: the diagnostics word becomes 1, the output of that call is
+ * unspecified, later calls return at once, and the communicator must be rebuilt (collectively)
+ * after the word has been read.  n_total, k_local and the strides must be multiples of 8;
+ * n_total / 32 (or / 64) must not exceed the SM count (every CTA has to be resident). */
+size_t b200attn_comm_bytes(int world, int max_tokens, int max_n);
+/* The launch geometry b200attn_rowlinear_allreduce picks on the current device: token rows of
+ * the MMA (32 / 64 / 128) and K splits (CTAs per cluster).  Staging units of one call are laid
+ * out by these two numbers; exposed for tests and tools that fill or read the staging area. */
+int b200attn_rowlinear_plan(int num_tokens, int n_total, int k_local, int* token_rows,
+                            int* k_splits);
+int b200attn_comm_alloc(size_t bytes, void** dev_ptr);
+int b200attn_comm_free(void* dev_ptr);
+int b200attn_comm_export(const void* dev_ptr, unsigned char* handle64);
+int b200attn_comm_import(const unsigned char* handle64, void** peer_ptr);
+int b200attn_comm_close(void* peer_ptr);
+int b200attn_rowlinear_allreduce(void* out, int64_t out_row_stride,
+                                 const void* x, int64_t x_row_stride,
+                                 const void* w, int64_t w_row_stride,
+                                 int num_tokens, int n_total, int k_local,
+                                 int rank, int world, void* const* comm_bufs,
+                                 int max_tokens, int max_n,
+                                 uint64_t peer_timeout_ns, void* stream);
+
 /* Copies the device diagnostics word of the current device to *out_host (synchronises the
  * stream) and clears it.  0 = no kernel reported a problem since the last read. */
 int b200attn_read_error_word(int32_t* out_host, void* stream);

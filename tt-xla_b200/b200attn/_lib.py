@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 
 _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libb200attn.so")
 _lib = None
@@ -67,6 +67,18 @@ SIGNATURES = {
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64, c_void_p,
          c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
          c_int64, c_float, c_int, c_void_p],
+    ),
+    "b200attn_comm_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "b200attn_rowlinear_plan": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200attn_comm_alloc": (c_int, [c_size_t, c_void_p]),
+    "b200attn_comm_free": (c_int, [c_void_p]),
+    "b200attn_comm_export": (c_int, [c_void_p, c_void_p]),
+    "b200attn_comm_import": (c_int, [c_void_p, c_void_p]),
+    "b200attn_comm_close": (c_int, [c_void_p]),
+    "b200attn_rowlinear_allreduce": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+         c_int, c_void_p, c_int, c_int, c_uint64, c_void_p],
     ),
     "b200attn_read_error_word": (c_int, [ctypes.POINTER(c_int32), c_void_p]),
 }

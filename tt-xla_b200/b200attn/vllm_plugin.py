@@ -13,6 +13,8 @@ math, the cache layout and the metadata derivation live there.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from vllm.v1.attention.backend import (AttentionBackend, AttentionCGSupport, AttentionImpl,
@@ -104,3 +106,45 @@ def register() -> None:
 
     register_backend(AttentionBackendEnum.CUSTOM,
                      "b200attn.vllm_plugin.B200VllmAttentionBackend")
+    if os.environ.get("B200ATTN_FUSED_ROW_PARALLEL", "0") == "1":
+        enable_fused_row_parallel()
+
+
+def enable_fused_row_parallel(max_tokens: int = 128, max_n: int = 8192) -> None:
+    """Points vLLM's RowParallelLinear (o_proj, down_proj: the layers the reference row-shards,
+    vllm_tt/vllm_distributed_utils.py:356-363) at the fused GEMM + all-reduce launch for bf16
+    batches of up to `max_tokens` rows; every other case keeps vLLM's GEMM + all-reduce.
+
+    The communicator of the tensor-parallel group is created at the first forward of any such
+    layer, which all ranks reach together during vLLM's eager profiling pass, well before decode
+    steps are captured into CUDA graphs.  Off unless B200ATTN_FUSED_ROW_PARALLEL=1."""
+    import torch
+    from vllm.distributed import get_tp_group
+    from vllm.model_executor.layers.linear import RowParallelLinear, UnquantizedLinearMethod
+
+    from . import tp_linear
+
+    if getattr(RowParallelLinear, "_b200attn_fused", False):
+        return
+    original = RowParallelLinear.forward
+    state = {"comm": None}
+
+    def forward(self, input_):
+        eligible = (
+            self.tp_size > 1 and self.reduce_results and self.input_is_parallel
+            and self.bias is None and isinstance(self.quant_method, UnquantizedLinearMethod)
+            and input_.dim() == 2 and input_.dtype == torch.bfloat16 and input_.is_cuda
+            and self.weight.dtype == torch.bfloat16 and self.weight.shape[0] <= max_n
+        )
+        if not eligible:
+            return original(self, input_)
+        if state["comm"] is None:
+            state["comm"] = tp_linear.RowLinearComm(
+                get_tp_group().cpu_group, max_n=max_n, max_tokens=max_tokens, device=input_.device)
+        if input_.shape[0] == 0 or input_.shape[0] > max_tokens or input_.stride(1) != 1:
+            return original(self, input_)
+        out = tp_linear.rowlinear_allreduce(input_, self.weight, state["comm"])
+        return out if not self.return_bias else (out, None)
+
+    RowParallelLinear.forward = forward
+    RowParallelLinear._b200attn_fused = True

@@ -5,12 +5,15 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
+#include <initializer_list>
 #include <mutex>
 
 #include "decode.cuh"
 #include "kv_scatter.cuh"
 #include "prefill.cuh"
 #include "rope_scatter.cuh"
+#include "rowlinear_ar.cuh"
 #include "step_metadata.cuh"
 
 namespace b200attn {
@@ -193,6 +196,55 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
                           const PrefillParams& p, int sm_count, cudaStream_t s) {
   return p.window > 0 ? launch_prefill_win<HD, BS, true>(tq, tk, tv, p, sm_count, s)
                       : launch_prefill_win<HD, BS, false>(tq, tk, tv, p, sm_count, s);
+}
+
+template <int NB, int S>
+static int launch_rowlinear(const CUtensorMap& tw, const CUtensorMap& tx, const RowLinearParams& p,
+                            int tiles, cudaStream_t s) {
+  using L = RowLinearSmem<NB>;
+  auto kern = rowlinear_allreduce_kernel<NB, S>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(S, static_cast<unsigned>(tiles), 1);
+  cfg.blockDim = dim3(kRlThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kTotalBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // Every cluster has to be resident at once (a CTA waits for the same CTA on its peers); the
+  // answer depends only on the instantiation, so it is asked once.
+  static int max_clusters[kMaxDevices] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (max_clusters[dev] == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      return B200ATTN_ERR_UNSUPPORTED;
+    }
+    max_clusters[dev] = n > 0 ? n : -1;
+  }
+  if (max_clusters[dev] < tiles) return B200ATTN_ERR_TOO_LARGE;
+  e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
+  return static_cast<int>(e);
+}
+
+template <int NB>
+static int launch_rowlinear_nb(int split, const CUtensorMap& tw, const CUtensorMap& tx,
+                               const RowLinearParams& p, int tiles, cudaStream_t s) {
+  switch (split) {
+    case 8: return launch_rowlinear<NB, 8>(tw, tx, p, tiles, s);
+    case 4: return launch_rowlinear<NB, 4>(tw, tx, p, tiles, s);
+    case 2: return launch_rowlinear<NB, 2>(tw, tx, p, tiles, s);
+    default: return launch_rowlinear<NB, 1>(tw, tx, p, tiles, s);
+  }
 }
 
 }  // namespace b200attn
@@ -654,6 +706,154 @@ int b200attn_read_error_word(int32_t* out_host, void* stream) {
   if (e == cudaSuccess) e = cudaMemsetAsync(dev->err_word, 0, sizeof(int), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   return static_cast<int>(e);
+}
+
+// ------------------------------------------------------------------------------ row-parallel
+// linear with fused all-reduce
+static inline int rl_token_rows(int tokens) { return tokens <= 32 ? 32 : (tokens <= 64 ? 64 : 128); }
+
+// bytes of one (parity, source rank) staging area: 8-byte units, one per bf16 pair
+static inline size_t rl_area_bytes(int max_tokens, int max_n) {
+  const size_t tiles = (static_cast<size_t>(max_n) + kRlTileN - 1) / kRlTileN;
+  return tiles * rl_token_rows(max_tokens) * (kRlTileN * 8 / 2);
+}
+
+size_t b200attn_comm_bytes(int world, int max_tokens, int max_n) {
+  if (world < 1 || world > kRlMaxWorld || max_tokens < 1 || max_tokens > kRlMaxTokens ||
+      max_n < 8)
+    return 0;
+  return kRlStageOff + static_cast<size_t>(2) * world * rl_area_bytes(max_tokens, max_n);
+}
+
+// K splits = CTAs per cluster: as many as keep every CTA resident and give each a K step.
+static void rl_plan(int sm_count, int n_total, int k_local, int* tiles, int* k_steps, int* split,
+                    int* per) {
+  *tiles = (n_total + kRlTileN - 1) / kRlTileN;
+  *k_steps = (k_local + kRlKStep - 1) / kRlKStep;
+  *split = 1;
+  *per = *k_steps;
+  for (int cand : {8, 4, 2}) {
+    const int c_per = (*k_steps + cand - 1) / cand;
+    if (*tiles * cand <= sm_count && (cand - 1) * c_per < *k_steps) {
+      *split = cand;
+      *per = c_per;
+      return;
+    }
+  }
+}
+
+int b200attn_rowlinear_plan(int num_tokens, int n_total, int k_local, int* token_rows,
+                            int* k_splits) {
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (!token_rows || !k_splits) return B200ATTN_ERR_NULL_POINTER;
+  if (num_tokens < 1 || num_tokens > kRlMaxTokens || n_total <= 0 || k_local <= 0)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  int tiles, k_steps, per;
+  rl_plan(dev->sm_count, n_total, k_local, &tiles, &k_steps, k_splits, &per);
+  *token_rows = rl_token_rows(num_tokens);
+  return B200ATTN_OK;
+}
+
+int b200attn_comm_alloc(size_t bytes, void** dev_ptr) {
+  if (!dev_ptr) return B200ATTN_ERR_NULL_POINTER;
+  if (bytes < kRlStageOff) return B200ATTN_ERR_BAD_ARGUMENT;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) {
+    if (p) cudaFree(p);
+    cudaGetLastError();
+    return static_cast<int>(e);
+  }
+  *dev_ptr = p;
+  return B200ATTN_OK;
+}
+
+int b200attn_comm_free(void* dev_ptr) {
+  return dev_ptr ? static_cast<int>(cudaFree(dev_ptr)) : B200ATTN_OK;
+}
+
+int b200attn_comm_export(const void* dev_ptr, unsigned char* handle64) {
+  if (!dev_ptr || !handle64) return B200ATTN_ERR_NULL_POINTER;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(dev_ptr));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return static_cast<int>(e);
+  }
+  memcpy(handle64, &h, 64);
+  return B200ATTN_OK;
+}
+
+int b200attn_comm_import(const unsigned char* handle64, void** peer_ptr) {
+  if (!handle64 || !peer_ptr) return B200ATTN_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return static_cast<int>(e);
+  }
+  *peer_ptr = p;
+  return B200ATTN_OK;
+}
+
+int b200attn_comm_close(void* peer_ptr) {
+  return peer_ptr ? static_cast<int>(cudaIpcCloseMemHandle(peer_ptr)) : B200ATTN_OK;
+}
+
+int b200attn_rowlinear_allreduce(void* out, int64_t out_row_stride, const void* x,
+                                 int64_t x_row_stride, const void* w, int64_t w_row_stride,
+                                 int num_tokens, int n_total, int k_local, int rank, int world,
+                                 void* const* comm_bufs, int max_tokens, int max_n,
+                                 uint64_t peer_timeout_ns, void* stream) {
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (!out || !x || !w) return B200ATTN_ERR_NULL_POINTER;
+  if (num_tokens < 0 || n_total <= 0 || k_local <= 0 || world < 1 || world > kRlMaxWorld ||
+      rank < 0 || rank >= world)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  if (num_tokens > kRlMaxTokens) return B200ATTN_ERR_TOO_LARGE;
+  if (num_tokens == 0) return B200ATTN_OK;
+  if ((n_total & 7) || (k_local & 7) || (out_row_stride & 7) || (x_row_stride & 7) ||
+      (w_row_stride & 7))
+    return B200ATTN_ERR_UNSUPPORTED;
+  if (!aligned16(out) || !aligned16(x) || !aligned16(w)) return B200ATTN_ERR_MISALIGNED;
+  int tiles, k_steps, split, per;
+  rl_plan(dev->sm_count, n_total, k_local, &tiles, &k_steps, &split, &per);
+  if (tiles > dev->sm_count) return B200ATTN_ERR_TOO_LARGE;
+  RowLinearParams p{};
+  if (world > 1) {
+    if (!comm_bufs) return B200ATTN_ERR_NULL_POINTER;
+    if (num_tokens > max_tokens || n_total > max_n || max_tokens > kRlMaxTokens)
+      return B200ATTN_ERR_WORKSPACE;
+    for (int r = 0; r < world; ++r) {
+      if (!comm_bufs[r]) return B200ATTN_ERR_NULL_POINTER;
+      p.comm[r] = static_cast<uint8_t*>(comm_bufs[r]);
+    }
+  }
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_row_stride = out_row_stride;
+  p.num_tokens = num_tokens;
+  p.n_total = n_total;
+  p.k_steps = k_steps;
+  p.steps_per_split = per;
+  p.rank = rank;
+  p.world = world;
+  p.src_stride = world > 1 ? rl_area_bytes(max_tokens, max_n) : 0;
+  p.peer_timeout_ns = peer_timeout_ns ? peer_timeout_ns : 10ull * 1000 * 1000 * 1000;
+  p.err_word = dev->err_word;
+  const int nb = rl_token_rows(num_tokens);
+  CUtensorMap tw, tx;
+  if (int rc = make_map(&tw, w, n_total, k_local, w_row_stride, kRlTileN)) return rc;
+  if (int rc = make_map(&tx, x, num_tokens, k_local, x_row_stride, nb)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (nb == 32) return launch_rowlinear_nb<32>(split, tw, tx, p, tiles, s);
+  if (nb == 64) return launch_rowlinear_nb<64>(split, tw, tx, p, tiles, s);
+  return launch_rowlinear_nb<128>(split, tw, tx, p, tiles, s);
 }
 
 }  // extern "C"
