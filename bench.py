@@ -460,9 +460,9 @@ def run_rowlinear_bench(args):
         x = torch.randn(tokens, kl, generator=g, device=device).to(torch.bfloat16)
         out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device)
 
-        def fused():
+        def fused(mode=0):
             for w in ws:
-                tp_linear.rowlinear_allreduce(x, w, comm, out=out)
+                tp_linear.rowlinear_allreduce(x, w, comm, out=out, reduce_mode=mode)
 
         def stock():
             for w in ws:
@@ -491,10 +491,14 @@ def run_rowlinear_bench(args):
 
         us_stock = timed(stock)
         us_fused = timed(fused)
+        by_mode = {}
+        if world > 2:       # both exchange schemes, for the record (the default picks two shots)
+            by_mode = {"one_shot_us": round(timed(lambda: fused(1)), 2),
+                       "two_shot_us": round(timed(lambda: fused(2)), 2)}
         wbytes = hidden * kl * 2
         results[name] = {"k_local": kl, "fused_us": round(us_fused, 2), "stock_us": round(us_stock, 2),
                          "weight_gbs_fused": round(wbytes / us_fused / 1e3, 1),
-                         "weight_gbs_stock": round(wbytes / us_stock / 1e3, 1)}
+                         "weight_gbs_stock": round(wbytes / us_stock / 1e3, 1), **by_mode}
     word = ops.read_error_word()
     if comm is not None:
         dist.barrier()

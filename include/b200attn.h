@@ -308,6 +308,11 @@ int b200attn_prefill_ex(void* out, int64_t out_row_stride,
  * in the calling process (own buffer at [rank]); with world == 1 it may be NULL and the call is
  * a plain GEMM.
  *
+ * reduce_mode: 1 = one shot (every rank sends its partial to every peer and adds all of them up),
+ * 2 = two shots (each tile share has an owner rank that adds the partials and sends the result
+ * back, so a rank's NVLink traffic does not grow with the number of ranks), 0 = one shot for two
+ * ranks, two shots beyond.
+ *
  * All ranks must issue the same sequence of calls with the same shapes on one stream each.  The
  * call is asynchronous and allocation-free.  A peer that does not arrive within peer_timeout_ns
  * (0 = 10 s) makes the kernel give up: the diagnostics word becomes 1, the output of that call is
@@ -330,7 +335,7 @@ int b200attn_rowlinear_allreduce(void* out, int64_t out_row_stride,
                                  const void* w, int64_t w_row_stride,
                                  int num_tokens, int n_total, int k_local,
                                  int rank, int world, void* const* comm_bufs,
-                                 int max_tokens, int max_n,
+                                 int max_tokens, int max_n, int reduce_mode,
                                  uint64_t peer_timeout_ns, void* stream);
 
 /* Copies the device diagnostics word of the current device to *out_host (synchronises the

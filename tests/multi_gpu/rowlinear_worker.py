@@ -33,8 +33,9 @@ def main() -> int:
         kl = k_full // world
         xs = x[:, rank * kl:(rank + 1) * kl].contiguous().cuda()
         ws = w[:, rank * kl:(rank + 1) * kl].contiguous().cuda()
+        mode = (0, 1, 2)[i % 3]                    # automatic, one shot, two shots
         for rep in range(3):                      # back-to-back calls exercise both parities
-            out = tp_linear.rowlinear_allreduce(xs, ws, comm, peer_timeout_s=5.0)
+            out = tp_linear.rowlinear_allreduce(xs, ws, comm, peer_timeout_s=5.0, reduce_mode=mode)
         torch.cuda.synchronize()
         # what every rank must return: its peers' and its own partial products rounded to bf16,
         # added in rank order in fp32 (one more rounding at the end)

@@ -78,7 +78,7 @@ SIGNATURES = {
     "b200attn_rowlinear_allreduce": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
-         c_int, c_void_p, c_int, c_int, c_uint64, c_void_p],
+         c_int, c_void_p, c_int, c_int, c_int, c_uint64, c_void_p],
     ),
     "b200attn_read_error_word": (c_int, [ctypes.POINTER(c_int32), c_void_p]),
 }

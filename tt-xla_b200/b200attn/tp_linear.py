@@ -46,7 +46,8 @@ def plan(num_tokens: int, n: int, k_local: int) -> tuple[int, int]:
 
 
 def area_bytes(max_tokens: int, max_n: int) -> int:
-    """Bytes of one (parity, source rank) staging area: 8-byte units {bf16 pair, epoch} laid out
+    """Bytes of one staging area (per parity: one area per source rank, then one for two-shot
+    results): 8-byte units {bf16 pair, epoch} laid out
     [tile * splits + share][pair of the share][column of the tile]."""
     rows = 32 if max_tokens <= 32 else (64 if max_tokens <= 64 else 128)
     return ((max_n + TILE_N - 1) // TILE_N) * rows * (TILE_N * 8 // 2)
@@ -125,11 +126,13 @@ def rowlinear_allreduce(
     comm: Optional[RowLinearComm],
     out: Optional[torch.Tensor] = None,
     peer_timeout_s: float = 0.0,
+    reduce_mode: int = 0,
 ) -> torch.Tensor:
     """out[t, n] = sum over ranks of bf16(x_r[t, :] @ weight_r[n, :]), x_r [tokens <= 128, K/world]
     bf16, weight_r [N, K/world] bf16 (this rank's slices); every rank of `comm` calls it with its
     own slices and gets the same bf16 [tokens, N] (fp32 accumulation inside each product and
-    across ranks).  `comm=None` is the single-rank GEMM."""
+    across ranks).  `comm=None` is the single-rank GEMM.  `reduce_mode`: 0 automatic, 1 one
+    shot, 2 two shots (see include/b200attn.h)."""
     _need_cuda(x, weight)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
         raise ValueError(f"x [tokens, K] and weight [N, K] expected, got {tuple(x.shape)} and "
@@ -153,7 +156,7 @@ def rowlinear_allreduce(
             weight.stride(0), tokens, n, k, comm.rank if comm is not None else 0, world,
             comm._ptr_array if comm is not None else None,
             comm.max_tokens if comm is not None else 0, comm.max_n if comm is not None else 0,
-            int(peer_timeout_s * 1e9), _stream(x),
+            int(reduce_mode), int(peer_timeout_s * 1e9), _stream(x),
         ),
     )
     return out

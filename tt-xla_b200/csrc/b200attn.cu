@@ -211,13 +211,17 @@ static int launch_rowlinear(const CUtensorMap& tw, const CUtensorMap& tx, const 
   cfg.blockDim = dim3(kRlThreads, 1, 1);
   cfg.dynamicSmemBytes = L::kTotalBytes;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // Programmatic dependent launch: CTAs may start (and fetch weights) while the kernel before
+  // drains; the kernel waits for that kernel's completion before it touches anything else.
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   // Every cluster has to be resident at once (a CTA waits for the same CTA on its peers); the
   // answer depends only on the instantiation, so it is asked once.
   static int max_clusters[kMaxDevices] = {};
@@ -722,7 +726,7 @@ size_t b200attn_comm_bytes(int world, int max_tokens, int max_n) {
   if (world < 1 || world > kRlMaxWorld || max_tokens < 1 || max_tokens > kRlMaxTokens ||
       max_n < 8)
     return 0;
-  return kRlStageOff + static_cast<size_t>(2) * world * rl_area_bytes(max_tokens, max_n);
+  return kRlStageOff + static_cast<size_t>(2) * (world + 1) * rl_area_bytes(max_tokens, max_n);
 }
 
 // K splits = CTAs per cluster: as many as keep every CTA resident and give each a K step.
@@ -809,12 +813,12 @@ int b200attn_rowlinear_allreduce(void* out, int64_t out_row_stride, const void* 
                                  int64_t x_row_stride, const void* w, int64_t w_row_stride,
                                  int num_tokens, int n_total, int k_local, int rank, int world,
                                  void* const* comm_bufs, int max_tokens, int max_n,
-                                 uint64_t peer_timeout_ns, void* stream) {
+                                 int reduce_mode, uint64_t peer_timeout_ns, void* stream) {
   DeviceInfo* dev;
   if (int rc = get_device(&dev)) return rc;
   if (!out || !x || !w) return B200ATTN_ERR_NULL_POINTER;
   if (num_tokens < 0 || n_total <= 0 || k_local <= 0 || world < 1 || world > kRlMaxWorld ||
-      rank < 0 || rank >= world)
+      rank < 0 || rank >= world || reduce_mode < 0 || reduce_mode > 2)
     return B200ATTN_ERR_BAD_ARGUMENT;
   if (num_tokens > kRlMaxTokens) return B200ATTN_ERR_TOO_LARGE;
   if (num_tokens == 0) return B200ATTN_OK;
@@ -844,6 +848,7 @@ int b200attn_rowlinear_allreduce(void* out, int64_t out_row_stride, const void* 
   p.rank = rank;
   p.world = world;
   p.src_stride = world > 1 ? rl_area_bytes(max_tokens, max_n) : 0;
+  p.two_shot = reduce_mode == 0 ? (world > 2) : (reduce_mode == 2);
   p.peer_timeout_ns = peer_timeout_ns ? peer_timeout_ns : 10ull * 1000 * 1000 * 1000;
   p.err_word = dev->err_word;
   const int nb = rl_token_rows(num_tokens);

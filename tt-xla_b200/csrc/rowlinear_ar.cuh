@@ -63,7 +63,8 @@ struct RowLinearParams {
   int k_steps;               // 64-wide K steps of this rank's slice
   int steps_per_split;       // K steps per CTA of a cluster (the last CTA may get fewer)
   int rank, world;
-  size_t src_stride;         // bytes of one (parity, source rank) staging area
+  int two_shot;              // 0: every rank reduces everything; 1: reduce at a slot's owner
+  size_t src_stride;         // bytes of one staging area; world + 1 areas per parity
   uint8_t* comm[kRlMaxWorld];   // communicator buffer of every rank as mapped here; own at [rank]
   uint64_t peer_timeout_ns;
   int* err_word;
@@ -91,10 +92,12 @@ struct RowLinearSmem {
 };
 
 // One 8-byte unit: two bf16 partial sums (token rows t, t+1 of one column) and the call's epoch.
-// Units of one (parity, source rank) area: [slot = tile * S + share][pair of the share][column].
+// Areas per parity: one per source rank, then one for results (two-shot mode).  Units of one
+// area: [slot = tile * S + share][pair of the share][column].
 __device__ __forceinline__ uint2* rl_unit(uint8_t* comm, const RowLinearParams& p, uint32_t parity,
                                           int src, int slot, int pairs_per_share, int pair, int col) {
-  uint8_t* area = comm + kRlStageOff + (static_cast<size_t>(parity) * p.world + src) * p.src_stride;
+  uint8_t* area =
+      comm + kRlStageOff + (static_cast<size_t>(parity) * (p.world + 1) + src) * p.src_stride;
   return reinterpret_cast<uint2*>(area) +
          (static_cast<size_t>(slot) * pairs_per_share + pair) * kRlTileN + col;
 }
@@ -128,6 +131,11 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Programmatic dependent launch: blocks until the kernels this launch depends on have completed
+// and their writes are visible (a no-op for an ordinary launch).
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
@@ -173,10 +181,6 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
-    // A wait of an earlier launch ran out: the ranks are no longer in step.  Skip the work but
-    // keep every barrier, so that the other CTAs of the cluster are not left waiting.
-    *dead_slot = *reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout;
-    *epoch_slot = p.world > 1 ? *reinterpret_cast<volatile uint32_t*>(&hdr->epoch) + 1u : 1u;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -187,26 +191,30 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
   __syncthreads();
   tc_fence_after_sync();
   cluster_arrive();     // #0: this CTA is up (its shared memory may be stored to from now on)
-#ifdef B200ATTN_RL_TIMING
-  if (p.world > 1 && threadIdx.x == 64)
-    (reinterpret_cast<uint64_t*>(p.comm[p.rank] + kRlStageOff + p.rank * p.src_stride) +
-     (blockIdx.y * S + blockIdx.x) * 8)[0] = global_timer_ns();
-#endif
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t epoch = *epoch_slot;
-  const uint32_t parity = epoch & 1u;
-  const bool dead = *dead_slot != 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && !dead) {
+    if (lane == 0) {
       prefetch_tensormap(&tm_w);
       prefetch_tensormap(&tm_x);
       const uint64_t pol_x = l2_policy_evict_last();
       const uint64_t pol_w = l2_policy_evict_first();
-      for (int i = 0; i < my_steps; ++i) {
+      // The weight does not depend on the kernels before this one: its first stages are on
+      // their way while those kernels drain (when the launch is a programmatic dependent one).
+      const int ahead = min(my_steps, kStages);
+      for (int i = 0; i < ahead; ++i) {
+        mbar_arrive_expect_tx(&full[i], L::kStageBytes);
+        tma_load_2d(smem + L::kWOff + i * L::kWBytes, &tm_w, &full[i], (ks_begin + i) * kRlKStep,
+                    n0, pol_w);
+      }
+      grid_dependency_wait();
+      for (int i = 0; i < ahead; ++i)
+        tma_load_2d(smem + L::kXOff + i * L::kXBytes, &tm_x, &full[i], (ks_begin + i) * kRlKStep, 0,
+                    pol_x);
+      for (int i = ahead; i < my_steps; ++i) {
         const int slot = i % kStages;
-        if (i >= kStages) mbar_wait(&empty[slot], ((i / kStages) & 1) ^ 1, abort_flag, p.err_word);
+        mbar_wait(&empty[slot], ((i / kStages) & 1) ^ 1, abort_flag, p.err_word);
         mbar_arrive_expect_tx(&full[slot], L::kStageBytes);
         const int k0 = (ks_begin + i) * kRlKStep;
         tma_load_2d(smem + L::kWOff + slot * L::kWBytes, &tm_w, &full[slot], k0, n0, pol_w);
@@ -223,7 +231,7 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version, SW128
     auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
     const bool leader = lane == 0;
-    if (!dead) {
+    {
       for (int i = 0; i < my_steps; ++i) {
         const int slot = i % kStages;
         mbar_wait(&full[slot], (i / kStages) & 1, abort_flag, p.err_word);
@@ -251,20 +259,21 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     const int col = (warp & 3) * 32 + lane;                // tensor-memory lane == output column
     const bool col_ok = n0 + col < p.n_total;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    if (!dead) {
-      mbar_wait(acc_full, 0, abort_flag, p.err_word);
-      tc_fence_after_sync();
+    // Everything below reads or writes memory other kernels touch: wait for them first.
+    grid_dependency_wait();
+    if (et == 0) {
+      // A wait of an earlier launch ran out: the ranks are no longer in step.  The GEMM still
+      // runs (its loads are already on their way), but nothing is published or waited for.
+      *dead_slot = *reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout;
+      *epoch_slot = p.world > 1 ? *reinterpret_cast<volatile uint32_t*>(&hdr->epoch) + 1u : 1u;
     }
-#ifdef B200ATTN_RL_TIMING
-    uint64_t* stamps = reinterpret_cast<uint64_t*>(own + kRlStageOff + p.rank * p.src_stride) +
-                       (tile * S + split) * 8;
-    const bool stamp = p.world > 1 && et == 0;
-    if (stamp) stamps[1] = global_timer_ns();
-#endif
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const uint32_t epoch = *epoch_slot;
+    const uint32_t parity = epoch & 1u;
+    const bool dead = *dead_slot != 0;
+    mbar_wait(acc_full, 0, abort_flag, p.err_word);
+    tc_fence_after_sync();
     cluster_wait();     // #0: every CTA of the cluster is up
-#ifdef B200ATTN_RL_TIMING
-    if (stamp) stamps[2] = global_timer_ns();
-#endif
     if (!dead) {
       // split-K: token row t of this CTA's D goes to CTA t / kShare, into its slab of our rows
       const uint32_t xch_addr = smem_u32(xch) + static_cast<uint32_t>(split * kShare * kRlTileN + col) * 4u;
@@ -292,9 +301,6 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     __syncwarp();
     cluster_arrive();   // #1: every piece and every health word has been stored
     cluster_wait();
-#ifdef B200ATTN_RL_TIMING
-    if (stamp) stamps[3] = global_timer_ns();
-#endif
     const int t_begin = split * kShare;
     float part[kShare];
     bool healthy = true;
@@ -321,33 +327,38 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
             o[static_cast<int64_t>(i) * p.out_row_stride] = __float2bfloat16_rn(part[i]);
       }
     } else {
+      // One shot (two ranks): every rank sends its partial to every peer and reduces everything.
+      // Two shots (more ranks): (tile, share) `slot` has an owner rank; the others send their
+      // partial to the owner only, the owner reduces and sends the bf16 result back to everyone,
+      // so a rank's traffic stays about two partials whatever the number of ranks.
+      const int owner = p.two_shot ? slot % p.world : -1;
+      const bool i_reduce = owner < 0 || owner == p.rank;     // this CTA adds the partials up
+      const int result_area = p.world;                        // area index after the ranks' own
       uint32_t mine[kPairs];
 #pragma unroll
       for (int u = 0; u < kPairs; ++u) mine[u] = pack_bf16x2(part[2 * u], part[2 * u + 1]);
-      if (active) {
+      if (active && (owner < 0 || owner != p.rank)) {
         for (int peer = 0; peer < p.world; ++peer) {
-          if (peer == p.rank) continue;
+          if (peer == p.rank || (owner >= 0 && peer != owner)) continue;
           uint2* dst = rl_unit(p.comm[peer], p, parity, p.rank, slot, kPairs, 0, col);
 #pragma unroll
           for (int u = 0; u < kPairs; ++u)
             if (t_begin + 2 * u < p.num_tokens) st_u2(dst + u * kRlTileN, mine[u], epoch);
         }
       }
-#ifdef B200ATTN_RL_TIMING
-    if (stamp) stamps[4] = global_timer_ns();
-#endif
       constexpr int kChunk = kPairs < 8 ? kPairs : 8;
       bool gave_up = !active;
 #pragma unroll
       for (int c = 0; c < kPairs; c += kChunk) {
         uint2 got[kRlMaxWorld][kChunk];
-        // a unit is wanted if it belongs to a peer of this call and to a live token row
+        // wanted: the partial of every peer when this CTA reduces, else the owner's result
+        // (kept in row 0)
 #pragma unroll
         for (int src = 0; src < kRlMaxWorld; ++src)
 #pragma unroll
           for (int u = 0; u < kChunk; ++u) {
-            const bool wanted = src < p.world && src != p.rank && !gave_up &&
-                                t_begin + 2 * (c + u) < p.num_tokens;
+            const bool from_src = i_reduce ? (src < p.world && src != p.rank) : (src == 0);
+            const bool wanted = from_src && !gave_up && t_begin + 2 * (c + u) < p.num_tokens;
             got[src][u].x = 0u;
             got[src][u].y = wanted ? epoch - 1u : epoch;
           }
@@ -357,8 +368,9 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
         for (uint32_t round = 1;; ++round) {
 #pragma unroll
           for (int src = 0; src < kRlMaxWorld; ++src) {
-            if (src < p.world) {
-              const uint2* from = rl_unit(own, p, parity, src, slot, kPairs, c, col);
+            if (i_reduce ? src < p.world : src == 0) {
+              const uint2* from =
+                  rl_unit(own, p, parity, i_reduce ? src : result_area, slot, kPairs, c, col);
 #pragma unroll
               for (int u = 0; u < kChunk; ++u)
                 if (got[src][u].y != epoch) got[src][u] = ld_volatile_u2(from + u * kRlTileN);
@@ -391,24 +403,36 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
           for (int u = 0; u < kChunk; ++u) {
             const int t = t_begin + 2 * (c + u);
             if (t >= p.num_tokens) continue;
-            float a0 = 0.f, a1 = 0.f;
+            uint32_t res;
+            if (i_reduce) {
+              float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-            for (int src = 0; src < kRlMaxWorld; ++src) {
-              if (src < p.world) {
-                const uint32_t v = (src == p.rank) ? mine[c + u] : got[src][u].x;
-                a0 += bf16_lo(v);
-                a1 += bf16_hi(v);
+              for (int src = 0; src < kRlMaxWorld; ++src) {
+                if (src < p.world) {
+                  const uint32_t v = (src == p.rank) ? mine[c + u] : got[src][u].x;
+                  a0 += bf16_lo(v);
+                  a1 += bf16_hi(v);
+                }
               }
+              res = pack_bf16x2(a0, a1);
+              if (owner >= 0) {
+                for (int peer = 0; peer < p.world; ++peer)
+                  if (peer != p.rank)
+                    st_u2(rl_unit(p.comm[peer], p, parity, result_area, slot, kPairs, c + u, col),
+                          res, epoch);
+              }
+            } else {
+              res = got[0][u].x;
             }
-            o[static_cast<int64_t>(2 * (c + u)) * p.out_row_stride] = __float2bfloat16_rn(a0);
+            unsigned short* o16 = reinterpret_cast<unsigned short*>(o);
+            o16[static_cast<int64_t>(2 * (c + u)) * p.out_row_stride] =
+                static_cast<unsigned short>(res & 0xffffu);
             if (t + 1 < p.num_tokens)
-              o[static_cast<int64_t>(2 * (c + u) + 1) * p.out_row_stride] = __float2bfloat16_rn(a1);
+              o16[static_cast<int64_t>(2 * (c + u) + 1) * p.out_row_stride] =
+                  static_cast<unsigned short>(res >> 16);
           }
         }
       }
-#ifdef B200ATTN_RL_TIMING
-    if (stamp) stamps[5] = global_timer_ns();
-#endif
     }
     __syncwarp();
   }
@@ -423,12 +447,8 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     // last CTA out publishes the epoch for the next call (the next launch on the stream reads it)
     if (atomicAdd(&hdr->ticket, 1u) == gridDim.x * gridDim.y - 1) {
       hdr->ticket = 0;
-      *reinterpret_cast<volatile uint32_t*>(&hdr->epoch) = epoch;
+      *reinterpret_cast<volatile uint32_t*>(&hdr->epoch) = *epoch_slot;
     }
-#ifdef B200ATTN_RL_TIMING
-    (reinterpret_cast<uint64_t*>(p.comm[p.rank] + kRlStageOff + p.rank * p.src_stride) +
-     (blockIdx.y * S + blockIdx.x) * 8)[6] = global_timer_ns();
-#endif
   }
 }
 
