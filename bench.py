@@ -60,6 +60,9 @@ WORKLOADS = {
     # profiler captures run on (268 MB of KV: larger than L2, small enough to replay)
     "c4s": dict(nq=64, nkv=8, hd=128, bs=64, users=8, ctx_lo=8192, ctx_hi=8192,
                 desc="c4_small_decode_llama70b_B8_L8192"),
+    # config 4 over an fp8 (e4m3) cache: half the bytes per token
+    "c4f8": dict(nq=64, nkv=8, hd=128, bs=64, users=32, ctx_lo=32768, ctx_hi=32768,
+                 kv_dtype="fp8_e4m3", desc="c4_long_context_decode_llama70b_B32_L32768_fp8kv"),
 }
 
 
@@ -131,25 +134,27 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def decode_algorithmic_bytes(ctx_lens: torch.Tensor, nq: int, nkv: int, hd: int, bs: int) -> int:
+def decode_algorithmic_bytes(ctx_lens: torch.Tensor, nq: int, nkv: int, hd: int, bs: int,
+                             kv_elem_bytes: int = 2) -> int:
     """K and V rows of every context read once (the G query heads of a KV head share them),
     q read and o written, page-table entries and positions read."""
     users = ctx_lens.numel()
-    kv = int(ctx_lens.sum()) * 2 * nkv * hd * 2
+    kv = int(ctx_lens.sum()) * 2 * nkv * hd * kv_elem_bytes
     qo = 2 * users * nq * hd * 2
     meta = int(((ctx_lens + bs - 1) // bs).sum()) * 4 + 4 * users
     return kv + qo + meta
 
 
-def gen_cache(nb: int, nkv: int, bs: int, hd: int, seed: int, device) -> torch.Tensor:
+def gen_cache(nb: int, nkv: int, bs: int, hd: int, seed: int, device,
+              dtype=torch.bfloat16) -> torch.Tensor:
     """N(0,1) cache generated block-range by block-range so the fp32 temporaries stay small."""
     g = torch.Generator(device=device).manual_seed(seed)
-    out = torch.empty((nb, nkv, bs, hd), dtype=torch.bfloat16, device=device)
+    out = torch.empty((nb, nkv, bs, hd), dtype=dtype, device=device)
     step = max(1, (256 << 20) // (nkv * bs * hd * 4))
     for b0 in range(0, nb, step):
         b1 = min(nb, b0 + step)
         out[b0:b1] = torch.randn((b1 - b0, nkv, bs, hd), generator=g, device=device,
-                                 dtype=torch.float32).to(torch.bfloat16)
+                                 dtype=torch.float32).to(dtype)
     return out
 
 
@@ -190,8 +195,9 @@ def make_decode_workload(wl: dict, rank: int, world: int, device):
     nb = users * nblk
     page_table = torch.randperm(nb, generator=g).reshape(users, nblk).to(torch.int32)
     nkv_l, nq_l = nkv // world, nq // world
-    k_cache = gen_cache(nb, nkv_l, bs, hd, 100 + rank, device)
-    v_cache = gen_cache(nb, nkv_l, bs, hd, 200 + rank, device)
+    kv_dtype = torch.float8_e4m3fn if wl.get("kv_dtype") == "fp8_e4m3" else torch.bfloat16
+    k_cache = gen_cache(nb, nkv_l, bs, hd, 100 + rank, device, kv_dtype)
+    v_cache = gen_cache(nb, nkv_l, bs, hd, 200 + rank, device, kv_dtype)
     gq = torch.Generator().manual_seed(300 + rank)
     host = dict(
         q=torch.randn(users, nq_l * hd, generator=gq).to(torch.bfloat16).pin_memory(),
@@ -281,7 +287,8 @@ def run_decode_bench(args, wl, rank, world, device):
         raise SystemExit(f"a kernel reported device error {err}")
 
     # ---- e2e: through the backend's forward with pinned host inputs, output read back
-    impl = B200AttentionBackendImpl(nq, hd, scale, nkv, None, None, "auto")
+    impl = B200AttentionBackendImpl(nq, hd, scale, nkv, None, None,
+                                    "fp8_e4m3" if wl.get("kv_dtype") == "fp8_e4m3" else "auto")
     kv = [w["k_cache"], w["v_cache"]]
     d_q = torch.empty_like(dev["q"])
     d_k = torch.empty_like(dev["k"])
@@ -317,8 +324,9 @@ def run_decode_bench(args, wl, rank, world, device):
     barrier(world)
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, device) / args.steps
 
-    full_bytes = decode_algorithmic_bytes(w["ctx"], wl["nq"], wl["nkv"], hd, bs)
-    rank_bytes = decode_algorithmic_bytes(w["ctx"], nq, nkv, hd, bs)
+    eb = w["k_cache"].element_size()
+    full_bytes = decode_algorithmic_bytes(w["ctx"], wl["nq"], wl["nkv"], hd, bs, eb)
+    rank_bytes = decode_algorithmic_bytes(w["ctx"], nq, nkv, hd, bs, eb)
     ms_per_step = total_ms / args.steps
     return dict(w=w, full_bytes=full_bytes, rank_bytes=rank_bytes, ms_per_step=ms_per_step,
                 decode_ms=decode_ms, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h, clocks=clocks,
@@ -767,7 +775,7 @@ def main():
     w = r["w"]
     del r["w"]
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and "kv_dtype" not in wl:
         w = None
         torch.cuda.empty_cache()
         cpu = run_cpu_baseline(wl)
@@ -786,6 +794,7 @@ def main():
             "config": {"workload": wl["desc"], "parallelism": f"kv_head_shard{world}",
                        "q_heads": wl["nq"], "kv_heads": wl["nkv"], "head_dim": wl["hd"],
                        "block_size": wl["bs"], "batch": wl["users"],
+                       "kv_cache_dtype": wl.get("kv_dtype", "bf16"),
                        "context": [wl["ctx_lo"], wl["ctx_hi"]], "num_splits": r["splits"],
                        "step": "KV write + split-KV decode + combine, replayed as one CUDA graph",
                        "eager_ms_per_step": round(r["eager_ms_per_step"], 4),

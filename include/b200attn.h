@@ -181,6 +181,42 @@ int b200attn_paged_decode(void* out, int64_t out_row_stride,
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * KV-cache element type.  The plugin maps the engine's kv_cache_dtype strings to torch dtypes
+ * (attention.py:42-51: "fp8" / "fp8_e4m3" -> float8_e4m3fn) and its cache write clamps to the
+ * finite range and casts (attention.py:692-700).  With B200ATTN_CACHE_FP8_E4M3 the three cache
+ * writes below do the same per element -- round to nearest even, saturate at +-448, NaN stays
+ * NaN, no scale factor -- into caches of one byte per element with the same
+ * [num_blocks, num_kv_heads, block_size, head_size] layout; b200attn_paged_decode_ex reads them.
+ * Prefill over an fp8 paged cache is not implemented (fresh-K/V prefill needs no cache). */
+enum b200attn_cache_dtype {
+  B200ATTN_CACHE_BF16 = 0,
+  B200ATTN_CACHE_FP8_E4M3 = 1
+};
+
+int b200attn_paged_update_cache_ex(void* k_cache, void* v_cache,
+                                   const void* k_new, const void* v_new,
+                                   int64_t new_token_stride,
+                                   const int32_t* update_indices,
+                                   const int32_t* page_table, int64_t page_table_stride,
+                                   int page_table_width,
+                                   int num_users, int num_kv_heads, int head_size,
+                                   int block_size, int64_t num_blocks, int cache_dtype,
+                                   void* stream);
+int b200attn_paged_fill_cache_ex(void* k_cache, void* v_cache,
+                                 const void* k_new, const void* v_new,
+                                 int64_t new_token_stride,
+                                 const int32_t* fill_page_table, int64_t page_table_stride,
+                                 int page_table_width, const int32_t* batch_idx,
+                                 int num_users, int tokens_per_user,
+                                 int num_kv_heads, int head_size, int block_size,
+                                 int64_t num_blocks, int cache_dtype, void* stream);
+int b200attn_kv_scatter_slots_ex(void* k_cache, void* v_cache,
+                                 const void* k_new, const void* v_new,
+                                 int64_t new_token_stride, const int64_t* slot_mapping,
+                                 int num_tokens, int num_kv_heads, int head_size, int block_size,
+                                 int64_t num_blocks, int cache_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Paged GQA decode attention for callers that cannot allocate device memory.
  * No counterpart in the reference: this entry point exists for hosts of this library that
  * must not call cudaMalloc around it -- code running inside a region where allocation is
@@ -219,7 +255,11 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride,
  *   sinks != NULL:      fp32 [num_q_heads]; head h's softmax gets one more column with logit
  *                       sinks[h] (in the scaled-score domain) that adds to the denominator only.
  * The reference's CPU branch ignores both arguments (custom_ops.py:1256-1312), so their parity
- * is checked against the published semantics, not against reference output. */
+ * is checked against the published semantics, not against reference output.
+ *   cache_dtype:        B200ATTN_CACHE_BF16, or B200ATTN_CACHE_FP8_E4M3 for caches written by the
+ *                       *_ex cache writes below (head_size 128 only): K and V are then one byte
+ *                       per element, unscaled, and are widened exactly inside the kernel; q, the
+ *                       softmax weights and the output stay 16-bit with fp32 accumulation. */
 int b200attn_paged_decode_ex(void* out, int64_t out_row_stride,
                              const void* q, int64_t q_row_stride,
                              const void* k_cache, const void* v_cache,
@@ -227,7 +267,7 @@ int b200attn_paged_decode_ex(void* out, int64_t out_row_stride,
                              int page_table_width, const int32_t* cur_pos,
                              int num_users, int num_q_heads, int num_kv_heads, int head_size,
                              int block_size, int64_t num_blocks, float scale,
-                             int sliding_window, const float* sinks,
+                             int sliding_window, const float* sinks, int cache_dtype,
                              int max_context_len, int num_splits,
                              void* workspace, size_t workspace_bytes, void* stream);
 

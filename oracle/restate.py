@@ -18,6 +18,13 @@ from typing import Optional
 import torch
 
 
+def quantize_kv_fp8(x: torch.Tensor) -> torch.Tensor:
+    """What the plugin's cache write does to K / V rows for an fp8 cache (attention.py:692-700):
+    clamp to the finite range of the cache dtype, then cast (round to nearest even).  No scale."""
+    info = torch.finfo(torch.float8_e4m3fn)
+    return x.float().clamp(info.min, info.max).to(torch.float8_e4m3fn)
+
+
 def paged_update_cache(
     cache: torch.Tensor,
     fill_value: torch.Tensor,
@@ -36,7 +43,9 @@ def paged_update_cache(
     block_offsets = torch.remainder(idx, block_size)
     user_range = torch.arange(num_users)
     blocks = page_table.to(torch.int64)[user_range, block_indices]  # negative columns wrap
-    cache[blocks, :, block_offsets, :] = fill_value[0, :, :num_heads, :]
+    rows = fill_value[0, :, :num_heads, :]
+    cache[blocks, :, block_offsets, :] = (
+        quantize_kv_fp8(rows) if cache.dtype == torch.float8_e4m3fn else rows)
     return cache
 
 
@@ -56,6 +65,8 @@ def paged_fill_cache(
         batch_idx = torch.arange(users, dtype=torch.int32)
     full = fill_seq_len // block_size
     tail = fill_seq_len % block_size
+    if cache.dtype == torch.float8_e4m3fn:
+        fill_value = quantize_kv_fp8(fill_value)
     for u in range(users):
         blocks = page_table[int(batch_idx[u])].to(torch.int64)
         fv = fill_value[u]

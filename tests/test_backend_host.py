@@ -44,7 +44,8 @@ def test_impl_constructor_errors():
         B200AttentionBackendImpl(8, 64, 0.125, 8, [1.0], None, "auto")
     with pytest.raises(NotImplementedError, match="encoder or decoder"):
         B200AttentionBackendImpl(8, 64, 0.125, 8, None, None, "auto", attn_type="encoder_decoder")
-    for kw in (dict(kv_cache_dtype="fp8"), dict(logits_soft_cap=30.0)):
+    for kw in (dict(kv_cache_dtype="fp8_e5m2"), dict(kv_cache_dtype="int8"),
+               dict(logits_soft_cap=30.0)):
         args = dict(num_heads=8, head_size=64, scale=0.125, num_kv_heads=8, alibi_slopes=None,
                     sliding_window=None, kv_cache_dtype="auto")
         args.update(kw)
@@ -56,6 +57,11 @@ def test_impl_constructor_errors():
         B200AttentionBackendImpl(8, 64, 0.125, 8, None, None, "auto", sinks=torch.zeros(4))
     impl = B200AttentionBackendImpl(8, 64, 0.125, 8, None, 128, "auto", sinks=torch.zeros(8))
     assert impl.sliding_window == 128 and impl.sinks is not None
+    assert impl.kv_cache_quantized_dtype is None
+    # attention.py:42-51: "fp8" and "fp8_e4m3" both mean float8_e4m3fn
+    for name in ("fp8", "fp8_e4m3"):
+        assert B200AttentionBackendImpl(8, 128, 0.1, 8, None, None, name).kv_cache_quantized_dtype \
+            is torch.float8_e4m3fn
 
 
 def test_normalize_shapes_and_messages():

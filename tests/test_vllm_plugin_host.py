@@ -36,7 +36,7 @@ def test_impl_accepts_vllm_constructor_arguments():
     out = torch.ones(4, 32 * 128)
     assert impl.forward(None, out, out, out, None, None, output=out).abs().sum() == 0
     with pytest.raises(NotImplementedError):
-        vllm_plugin.B200VllmAttentionImpl(32, 128, 0.088, num_kv_heads=8, kv_cache_dtype="fp8")
+        vllm_plugin.B200VllmAttentionImpl(32, 128, 0.088, num_kv_heads=8, kv_cache_dtype="fp8_e5m2")
 
 
 def test_fused_row_parallel_hook_is_idempotent_and_skips_single_rank_layers(monkeypatch):

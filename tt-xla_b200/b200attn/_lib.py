@@ -17,15 +17,30 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int,
          c_int, c_int, c_int, c_int, c_int64, c_void_p],
     ),
+    "b200attn_paged_update_cache_ex": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int,
+         c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p],
+    ),
     "b200attn_paged_fill_cache": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p,
          c_int, c_int, c_int, c_int, c_int, c_int64, c_void_p],
     ),
+    "b200attn_paged_fill_cache_ex": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p,
+         c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p],
+    ),
     "b200attn_kv_scatter_slots": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int,
          c_int64, c_void_p],
+    ),
+    "b200attn_kv_scatter_slots_ex": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int,
+         c_int64, c_int, c_void_p],
     ),
     "b200attn_build_step_metadata": (
         c_int,
@@ -47,7 +62,7 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int,
          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p, c_int,
-         c_int, c_void_p, c_size_t, c_void_p],
+         c_int, c_int, c_void_p, c_size_t, c_void_p],
     ),
     "b200attn_paged_decode_static": (
         c_int,

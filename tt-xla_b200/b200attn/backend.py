@@ -323,12 +323,15 @@ class B200AttentionBackendImpl:
                 f"B200 attention only supports encoder or decoder attention, but got {attn_type}."
             )
         self.attn_type = attn_type
+        # The reference maps the engine's names to torch dtypes (attention.py:42-51, 259-263).
+        # The CUDA kernels store bf16 or unscaled e4m3 and refuse the rest instead of silently
+        # converting.
         self.kv_cache_quantized_dtype = None
-        if kv_cache_dtype not in ("auto", "bfloat16"):
-            # The reference maps fp8/int8 names to torch dtypes (attention.py:259-263); the CUDA
-            # kernels store bf16 only and refuse the rest instead of silently converting.
+        if kv_cache_dtype in ("fp8", "fp8_e4m3"):
+            self.kv_cache_quantized_dtype = torch.float8_e4m3fn
+        elif kv_cache_dtype not in ("auto", "bfloat16"):
             raise NotImplementedError(
-                f"kv_cache_dtype {kv_cache_dtype!r} is not supported (bf16 cache only)"
+                f"kv_cache_dtype {kv_cache_dtype!r} is not supported (bfloat16 or fp8_e4m3 caches)"
             )
         if sliding_window is not None and int(sliding_window) <= 0:
             raise ValueError(f"sliding_window must be positive, got {sliding_window}")

@@ -18,6 +18,13 @@ from . import _lib
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 
+CACHE_BF16, CACHE_FP8_E4M3 = 0, 1     # enum b200attn_cache_dtype
+
+
+def _cache_dtype(cache: torch.Tensor) -> int:
+    return CACHE_FP8_E4M3 if cache.dtype == torch.float8_e4m3fn else CACHE_BF16
+
+
 def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -37,8 +44,8 @@ def _check_cache(k_cache: torch.Tensor, v_cache: torch.Tensor) -> tuple[int, int
             "k_cache and v_cache must both be [num_blocks, num_kv_heads, block_size, head_size]; "
             f"got {tuple(k_cache.shape)} and {tuple(v_cache.shape)}"
         )
-    if k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
-        raise ValueError("only bfloat16 caches are supported")
+    if k_cache.dtype != v_cache.dtype or k_cache.dtype not in (torch.bfloat16, torch.float8_e4m3fn):
+        raise ValueError("caches must both be bfloat16 or both be float8_e4m3fn")
     if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise ValueError("caches must be contiguous")
     nb, nkv, bs, hd = k_cache.shape
@@ -91,11 +98,11 @@ def paged_update_cache(
         raise ValueError("page_table rows and update_indices must be dense")
     L = _lib.lib()
     _lib.check(
-        "b200attn_paged_update_cache",
-        L.b200attn_paged_update_cache(
+        "b200attn_paged_update_cache_ex",
+        L.b200attn_paged_update_cache_ex(
             k_cache.data_ptr(), v_cache.data_ptr(), key.data_ptr(), value.data_ptr(), kstride,
             update_indices.data_ptr(), page_table.data_ptr(), page_table.stride(0),
-            page_table.shape[1], users, nkv, hd, bs, nb, _stream(k_cache),
+            page_table.shape[1], users, nkv, hd, bs, nb, _cache_dtype(k_cache), _stream(k_cache),
         ),
     )
 
@@ -131,12 +138,12 @@ def paged_fill_cache(
             raise ValueError("batch_idx must hold one dense entry per user")
     L = _lib.lib()
     _lib.check(
-        "b200attn_paged_fill_cache",
-        L.b200attn_paged_fill_cache(
+        "b200attn_paged_fill_cache_ex",
+        L.b200attn_paged_fill_cache_ex(
             k_cache.data_ptr(), v_cache.data_ptr(), key.data_ptr(), value.data_ptr(), nkv * hd,
             fill_page_table.data_ptr(), fill_page_table.stride(0), fill_page_table.shape[1],
             batch_idx.data_ptr() if batch_idx is not None else None,
-            users, tokens, nkv, hd, bs, nb, _stream(k_cache),
+            users, tokens, nkv, hd, bs, nb, _cache_dtype(k_cache), _stream(k_cache),
         ),
     )
 
@@ -164,10 +171,10 @@ def kv_scatter_slots(
         raise ValueError("fewer key/value rows than slots")
     L = _lib.lib()
     _lib.check(
-        "b200attn_kv_scatter_slots",
-        L.b200attn_kv_scatter_slots(
+        "b200attn_kv_scatter_slots_ex",
+        L.b200attn_kv_scatter_slots_ex(
             k_cache.data_ptr(), v_cache.data_ptr(), key.data_ptr(), value.data_ptr(), kstride,
-            slot_mapping.data_ptr(), n, nkv, hd, bs, nb, _stream(k_cache),
+            slot_mapping.data_ptr(), n, nkv, hd, bs, nb, _cache_dtype(k_cache), _stream(k_cache),
         ),
     )
 
@@ -316,7 +323,7 @@ def paged_decode(
             out_t.data_ptr(), ostride, q.data_ptr(), qstride, k_cache.data_ptr(),
             v_cache.data_ptr(), page_table.data_ptr(), page_table.stride(0), page_table.shape[1],
             cur_pos.data_ptr(), users, nq, nkv, hd, bs, nb, float(scale), int(sliding_window),
-            sinks.data_ptr() if sinks is not None else None, max_context_len,
+            sinks.data_ptr() if sinks is not None else None, _cache_dtype(k_cache), max_context_len,
             num_splits, ws.data_ptr() if ws is not None else None,
             ws.numel() * ws.element_size() if ws is not None else 0, _stream(query),
         ),
@@ -355,6 +362,10 @@ def prefill(
     paged = page_table is not None
     if paged:
         nb, nkv, bs, _hd = _check_cache(k_src, v_src)
+        if k_src.dtype == torch.float8_e4m3fn:
+            raise NotImplementedError(
+                "prefill over an fp8 paged cache is not implemented (decode and the cache writes "
+                "are); prefill the fresh bf16 K/V instead")
         if _hd != hd:
             raise ValueError("cache head_size differs from query head_size")
         _i32(page_table, "page_table")

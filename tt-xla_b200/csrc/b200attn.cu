@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "decode.cuh"
+#include "decode_fp8.cuh"
 #include "kv_scatter.cuh"
 #include "prefill.cuh"
 #include "rope_scatter.cuh"
@@ -96,6 +97,19 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ERR_TENSOR_MAP;
 }
 
+// e4m3 cache [rows, 128] (one byte per element): boxes of [box_rows x 128 bytes], 128-byte swizzle.
+static int make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows) {
+  const cuuint64_t dims[2] = {128, rows};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ERR_TENSOR_MAP;
+}
+
 static int check_cache_geometry(int num_kv_heads, int head_size, int block_size,
                                 int64_t num_blocks) {
   if (num_kv_heads <= 0 || num_blocks <= 0) return B200ATTN_ERR_BAD_ARGUMENT;
@@ -138,7 +152,10 @@ static int launch_scatter(int mode, ScatterParams& p, int head_size, void* strea
 
 static int fill_scatter_common(ScatterParams& p, void* k_cache, void* v_cache, const void* k_new,
                                const void* v_new, int64_t new_token_stride, int num_kv_heads,
-                               int head_size, int block_size, int64_t num_blocks) {
+                               int head_size, int block_size, int64_t num_blocks,
+                               int cache_dtype = B200ATTN_CACHE_BF16) {
+  if (cache_dtype != B200ATTN_CACHE_BF16 && cache_dtype != B200ATTN_CACHE_FP8_E4M3)
+    return B200ATTN_ERR_BAD_ARGUMENT;
   if (int rc = check_cache_geometry(num_kv_heads, head_size, block_size, num_blocks)) return rc;
   if (new_token_stride < static_cast<int64_t>(num_kv_heads) * head_size)
     return B200ATTN_ERR_BAD_ARGUMENT;
@@ -149,6 +166,7 @@ static int fill_scatter_common(ScatterParams& p, void* k_cache, void* v_cache, c
   p.k_new = static_cast<const uint4*>(k_new);
   p.v_new = static_cast<const uint4*>(v_new);
   p.new_token_stride_v = new_token_stride / 8;
+  p.cache_fp8 = cache_dtype == B200ATTN_CACHE_FP8_E4M3;
   p.num_kv_heads = num_kv_heads;
   p.block_size = block_size;
   p.num_blocks = num_blocks;
@@ -170,6 +188,26 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   if (p.num_splits > 1) {
     dim3 cgrid(p.num_q_heads, num_users);
     decode_combine_kernel<HD><<<cgrid, HD, 0, s>>>(p);
+    e = cudaGetLastError();
+  }
+  return static_cast<int>(e);
+}
+
+template <int BS, int STAGES>
+static int launch_decode_fp8(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p,
+                             int num_users, cudaStream_t s) {
+  using L = DecodeFp8Smem<BS, STAGES>;
+  auto kern = paged_decode_fp8_kernel<BS, STAGES>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid(p.num_splits, p.num_kv_heads, num_users);
+  kern<<<grid, kDecThreads, L::kTotalBytes, s>>>(tk, tv, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (p.num_splits > 1) {
+    dim3 cgrid(p.num_q_heads, num_users);
+    decode_combine_kernel<128><<<cgrid, 128, 0, s>>>(p);
     e = cudaGetLastError();
   }
   return static_cast<int>(e);
@@ -284,11 +322,23 @@ int b200attn_paged_update_cache(void* k_cache, void* v_cache, const void* k_new,
                                 int64_t page_table_stride, int page_table_width, int num_users,
                                 int num_kv_heads, int head_size, int block_size,
                                 int64_t num_blocks, void* stream) {
+  return b200attn_paged_update_cache_ex(
+      k_cache, v_cache, k_new, v_new, new_token_stride, update_indices, page_table,
+      page_table_stride, page_table_width, num_users, num_kv_heads, head_size, block_size,
+      num_blocks, B200ATTN_CACHE_BF16, stream);
+}
+
+int b200attn_paged_update_cache_ex(void* k_cache, void* v_cache, const void* k_new,
+                                const void* v_new, int64_t new_token_stride,
+                                const int32_t* update_indices, const int32_t* page_table,
+                                int64_t page_table_stride, int page_table_width, int num_users,
+                                int num_kv_heads, int head_size, int block_size,
+                                int64_t num_blocks, int cache_dtype, void* stream) {
   if (num_users < 0 || page_table_width <= 0) return B200ATTN_ERR_BAD_ARGUMENT;
   if (!update_indices || !page_table) return B200ATTN_ERR_NULL_POINTER;
   ScatterParams p;
   if (int rc = fill_scatter_common(p, k_cache, v_cache, k_new, v_new, new_token_stride,
-                                   num_kv_heads, head_size, block_size, num_blocks))
+                                   num_kv_heads, head_size, block_size, num_blocks, cache_dtype))
     return rc;
   p.positions = update_indices;
   p.page_table = page_table;
@@ -304,6 +354,18 @@ int b200attn_paged_fill_cache(void* k_cache, void* v_cache, const void* k_new, c
                               const int32_t* batch_idx, int num_users, int tokens_per_user,
                               int num_kv_heads, int head_size, int block_size,
                               int64_t num_blocks, void* stream) {
+  return b200attn_paged_fill_cache_ex(
+      k_cache, v_cache, k_new, v_new, new_token_stride, fill_page_table, page_table_stride,
+      page_table_width, batch_idx, num_users, tokens_per_user, num_kv_heads, head_size,
+      block_size, num_blocks, B200ATTN_CACHE_BF16, stream);
+}
+
+int b200attn_paged_fill_cache_ex(void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                              int64_t new_token_stride, const int32_t* fill_page_table,
+                              int64_t page_table_stride, int page_table_width,
+                              const int32_t* batch_idx, int num_users, int tokens_per_user,
+                              int num_kv_heads, int head_size, int block_size,
+                              int64_t num_blocks, int cache_dtype, void* stream) {
   if (num_users < 0 || tokens_per_user < 0 || page_table_width <= 0)
     return B200ATTN_ERR_BAD_ARGUMENT;
   if (!fill_page_table) return B200ATTN_ERR_NULL_POINTER;
@@ -311,7 +373,7 @@ int b200attn_paged_fill_cache(void* k_cache, void* v_cache, const void* k_new, c
     return B200ATTN_ERR_BAD_ARGUMENT;
   ScatterParams p;
   if (int rc = fill_scatter_common(p, k_cache, v_cache, k_new, v_new, new_token_stride,
-                                   num_kv_heads, head_size, block_size, num_blocks))
+                                   num_kv_heads, head_size, block_size, num_blocks, cache_dtype))
     return rc;
   p.page_table = fill_page_table;
   p.page_table_stride = page_table_stride;
@@ -326,11 +388,20 @@ int b200attn_kv_scatter_slots(void* k_cache, void* v_cache, const void* k_new, c
                               int64_t new_token_stride, const int64_t* slot_mapping,
                               int num_tokens, int num_kv_heads, int head_size, int block_size,
                               int64_t num_blocks, void* stream) {
+  return b200attn_kv_scatter_slots_ex(
+      k_cache, v_cache, k_new, v_new, new_token_stride, slot_mapping, num_tokens, num_kv_heads,
+      head_size, block_size, num_blocks, B200ATTN_CACHE_BF16, stream);
+}
+
+int b200attn_kv_scatter_slots_ex(void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                              int64_t new_token_stride, const int64_t* slot_mapping,
+                              int num_tokens, int num_kv_heads, int head_size, int block_size,
+                              int64_t num_blocks, int cache_dtype, void* stream) {
   if (num_tokens < 0) return B200ATTN_ERR_BAD_ARGUMENT;
   if (!slot_mapping) return B200ATTN_ERR_NULL_POINTER;
   ScatterParams p;
   if (int rc = fill_scatter_common(p, k_cache, v_cache, k_new, v_new, new_token_stride,
-                                   num_kv_heads, head_size, block_size, num_blocks))
+                                   num_kv_heads, head_size, block_size, num_blocks, cache_dtype))
     return rc;
   p.slot_mapping = slot_mapping;
   p.num_tokens = num_tokens;
@@ -475,8 +546,8 @@ int b200attn_paged_decode(void* out, int64_t out_row_stride, const void* q, int6
   return b200attn_paged_decode_ex(out, out_row_stride, q, q_row_stride, k_cache, v_cache,
                                   page_table, page_table_stride, page_table_width, cur_pos,
                                   num_users, num_q_heads, num_kv_heads, head_size, block_size,
-                                  num_blocks, scale, 0, nullptr, max_context_len, num_splits,
-                                  workspace, workspace_bytes, stream);
+                                  num_blocks, scale, 0, nullptr, B200ATTN_CACHE_BF16,
+                                  max_context_len, num_splits, workspace, workspace_bytes, stream);
 }
 
 int b200attn_paged_decode_ex(void* out, int64_t out_row_stride, const void* q,
@@ -485,9 +556,14 @@ int b200attn_paged_decode_ex(void* out, int64_t out_row_stride, const void* q,
                              int page_table_width, const int32_t* cur_pos, int num_users,
                              int num_q_heads, int num_kv_heads, int head_size, int block_size,
                              int64_t num_blocks, float scale, int sliding_window,
-                             const float* sinks, int max_context_len, int num_splits,
-                             void* workspace, size_t workspace_bytes, void* stream) {
+                             const float* sinks, int cache_dtype, int max_context_len,
+                             int num_splits, void* workspace, size_t workspace_bytes,
+                             void* stream) {
   if (sliding_window < 0 || !(scale > 0.f)) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (cache_dtype != B200ATTN_CACHE_BF16 && cache_dtype != B200ATTN_CACHE_FP8_E4M3)
+    return B200ATTN_ERR_BAD_ARGUMENT;
+  const bool fp8 = cache_dtype == B200ATTN_CACHE_FP8_E4M3;
+  if (fp8 && head_size != 128) return B200ATTN_ERR_UNSUPPORTED;
   if (!out || !q || !k_cache || !v_cache || !page_table || !cur_pos)
     return B200ATTN_ERR_NULL_POINTER;
   if (num_users < 0 || num_q_heads <= 0 || page_table_width <= 0 || num_splits < 0)
@@ -518,8 +594,13 @@ int b200attn_paged_decode_ex(void* out, int64_t out_row_stride, const void* q,
 
   CUtensorMap tk, tv;
   const uint64_t rows = static_cast<uint64_t>(num_blocks) * num_kv_heads * block_size;
-  if (int rc = make_map(&tk, k_cache, rows, head_size, head_size, block_size)) return rc;
-  if (int rc = make_map(&tv, v_cache, rows, head_size, head_size, block_size)) return rc;
+  if (fp8) {
+    if (int rc = make_map_u8(&tk, k_cache, rows, block_size)) return rc;
+    if (int rc = make_map_u8(&tv, v_cache, rows, block_size)) return rc;
+  } else {
+    if (int rc = make_map(&tk, k_cache, rows, head_size, head_size, block_size)) return rc;
+    if (int rc = make_map(&tv, v_cache, rows, head_size, head_size, block_size)) return rc;
+  }
 
   DecodeParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
@@ -547,6 +628,9 @@ int b200attn_paged_decode_ex(void* out, int64_t out_row_stride, const void* q,
     p.part_ml = reinterpret_cast<float2*>(static_cast<uint8_t*>(workspace) + o_bytes);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (fp8)
+    return block_size == 64 ? launch_decode_fp8<64, 6>(tk, tv, p, num_users, s)
+                            : launch_decode_fp8<32, 6>(tk, tv, p, num_users, s);
   if (head_size == 128 && block_size == 64) return launch_decode<128, 64, 3>(tk, tv, p, num_users, s);
   if (head_size == 128 && block_size == 32) return launch_decode<128, 32, 3>(tk, tv, p, num_users, s);
   if (head_size == 64 && block_size == 64) return launch_decode<64, 64, 4>(tk, tv, p, num_users, s);

@@ -1,7 +1,8 @@
 // KV-cache write: scatters new K and V rows into the paged caches.
 //
 // One (token, kv head) row of the cache is head_size*2 bytes contiguous, so every thread
-// moves one 16-byte vector and a warp's stores are fully coalesced.  K and V go in the same
+// moves one 16-byte vector and a warp's stores are fully coalesced (an e4m3 cache gets the
+// vector's 8 values as 8 bytes).  K and V go in the same
 // launch.  The three addressing forms differ only in how a token finds its block and offset.
 #pragma once
 #include "ptx.cuh"
@@ -32,8 +33,21 @@ struct ScatterParams {
   int block_size;
   int64_t num_blocks;
   int vec_per_head;           // head_size * 2 / 16
+  int cache_fp8;              // 1: the caches hold e4m3 (8 bytes per vector), 0: bf16
   int* err_word;
 };
+
+// 8 bf16 -> 8 e4m3, round to nearest even, saturating at +-448 (what clamping to the finite
+// range and casting does, attention.py:692-700); NaN stays NaN.
+__device__ __forceinline__ uint2 bf16x8_to_e4m3x8(const uint4 v) {
+  auto pair = [](uint32_t w) -> uint32_t {       // two bf16 -> two e4m3 in the low 16 bits
+    uint16_t r;
+    const float lo = __uint_as_float(w << 16), hi = __uint_as_float(w & 0xffff0000u);
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+  };
+  return make_uint2(pair(v.x) | (pair(v.y) << 16), pair(v.z) | (pair(v.w) << 16));
+}
 
 // Python-style floor division and modulo (the reference's CPU branch indexes with torch
 // `//` and `%`, which floor).
@@ -91,8 +105,13 @@ __global__ void __launch_bounds__(256) kv_scatter_kernel(const ScatterParams p) 
         ((blk * p.num_kv_heads + h) * p.block_size + off) * p.vec_per_head + v;
     const uint4 kv = __ldg(p.k_new + src);
     const uint4 vv = __ldg(p.v_new + src);
-    p.k_cache[dst] = kv;
-    p.v_cache[dst] = vv;
+    if (p.cache_fp8) {
+      reinterpret_cast<uint2*>(p.k_cache)[dst] = bf16x8_to_e4m3x8(kv);
+      reinterpret_cast<uint2*>(p.v_cache)[dst] = bf16x8_to_e4m3x8(vv);
+    } else {
+      p.k_cache[dst] = kv;
+      p.v_cache[dst] = vv;
+    }
   }
 }
 
