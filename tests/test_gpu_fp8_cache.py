@@ -16,7 +16,11 @@ FP8 = torch.float8_e4m3fn
 
 
 def _bits(t):
-    return t.view(torch.uint8)
+    """Byte image with the two NaN encodings of e4m3 (0x7f, 0xff) folded together: which one a
+    conversion produces for a NaN input carries no information."""
+    b = t.view(torch.uint8).clone()
+    b[b == 0xFF] = 0x7F
+    return b
 
 
 def _special_rows(shape, g):
