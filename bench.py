@@ -806,9 +806,12 @@ def main():
             "gpu_launches": r["launches"],
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-                         "traffic": traffic, "traffic_source": "ncu capture of the small case, scaled",
+                         "traffic": None if "kv_dtype" in wl else traffic,
+                         "traffic_source": "not captured for the fp8 kernel" if "kv_dtype" in wl
+                         else "ncu capture of the small case, scaled",
                          "peak_source": peaks["source"],
-                         "kernel": "paged_decode_splitkv_kernel + decode_combine_kernel",
+                         "kernel": ("paged_decode_fp8_kernel" if "kv_dtype" in wl
+                                    else "paged_decode_splitkv_kernel") + " + decode_combine_kernel",
                          "ms_per_launch": round(r["decode_ms"], 4),
                          "algorithmic_bytes_per_launch": r["rank_bytes"]},
             "cpu_baseline": cpu,
