@@ -60,6 +60,8 @@ WORKLOADS = {
     # profiler captures run on (268 MB of KV: larger than L2, small enough to replay)
     "c4s": dict(nq=64, nkv=8, hd=128, bs=64, users=8, ctx_lo=8192, ctx_hi=8192,
                 desc="c4_small_decode_llama70b_B8_L8192"),
+    "c4sf8": dict(nq=64, nkv=8, hd=128, bs=64, users=8, ctx_lo=8192, ctx_hi=8192,
+                  kv_dtype="fp8_e4m3", desc="c4_small_decode_llama70b_B8_L8192_fp8kv"),
     # config 4 over an fp8 (e4m3) cache: half the bytes per token
     "c4f8": dict(nq=64, nkv=8, hd=128, bs=64, users=32, ctx_lo=32768, ctx_hi=32768,
                  kv_dtype="fp8_e4m3", desc="c4_long_context_decode_llama70b_B32_L32768_fp8kv"),
