@@ -6,8 +6,8 @@
 Default workload ("c4"): long-context paged GQA decode with Llama-3.1-70B attention shapes
 (64 q heads, 8 kv heads, head_dim 128, bf16, batch 32, every context 32768 tokens, block 64),
 KV heads sharded across the N GPUs with no data-path collective.  One step = one decode pass of
-the hot path over the batch: the KV write of the new token (1 launch) and the split-KV decode
-attention (2 launches).  The headline value is decode-attention HBM GB/s: algorithmic bytes of
+the hot path over the batch: the KV write of the new token, done inside the split-KV decode
+launch, and the split combine (2 launches; 1 when the batch needs no split).  The headline value is decode-attention HBM GB/s: algorithmic bytes of
 the batch divided by the step time (max over ranks).
 
 One JSON line is printed by rank 0.  Besides the contract keys it carries
@@ -229,10 +229,9 @@ def run_decode_bench(args, wl, rank, world, device):
     splits = ops.decode_auto_splits(users, nkv, hd, w["max_ctx"])
 
     def step():
-        ops.paged_update_cache(w["k_cache"], w["v_cache"], k3, v3, dev["cache_position"],
-                               dev["page_table"])
         ops.paged_decode(q3, w["k_cache"], w["v_cache"], dev["page_table"], dev["cache_position"],
-                         scale=scale, out=out3, num_splits=splits, max_context_len=w["max_ctx"])
+                         scale=scale, out=out3, num_splits=splits, max_context_len=w["max_ctx"],
+                         new_key=k3, new_value=v3)
 
     ops.read_error_word()
     for _ in range(args.warmup):
@@ -250,11 +249,8 @@ def run_decode_bench(args, wl, rank, world, device):
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
     for i in range(args.steps):
-        ops.paged_update_cache(w["k_cache"], w["v_cache"], k3, v3, dev["cache_position"],
-                               dev["page_table"])
         ev[i][0].record()
-        ops.paged_decode(q3, w["k_cache"], w["v_cache"], dev["page_table"], dev["cache_position"],
-                         scale=scale, out=out3, num_splits=splits, max_context_len=w["max_ctx"])
+        step()
         ev[i][1].record()
     t1.record()
     barrier(world)
@@ -333,7 +329,7 @@ def run_decode_bench(args, wl, rank, world, device):
     return dict(w=w, full_bytes=full_bytes, rank_bytes=rank_bytes, ms_per_step=ms_per_step,
                 decode_ms=decode_ms, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h, clocks=clocks,
                 eager_ms_per_step=eager_ms / args.steps,
-                splits=splits, launches=3 * args.steps,
+                splits=splits, launches=(2 if splits > 1 else 1) * args.steps,
                 partial_bytes=ops.decode_workspace_bytes(users, nq, hd, splits))
 
 
@@ -798,7 +794,8 @@ def main():
                        "block_size": wl["bs"], "batch": wl["users"],
                        "kv_cache_dtype": wl.get("kv_dtype", "bf16"),
                        "context": [wl["ctx_lo"], wl["ctx_hi"]], "num_splits": r["splits"],
-                       "step": "KV write + split-KV decode + combine, replayed as one CUDA graph",
+                       "step": "split-KV decode launch that also writes the new K/V rows, + combine; replayed as "
+                               "one CUDA graph",
                        "eager_ms_per_step": round(r["eager_ms_per_step"], 4),
                        "l2": "inputs larger than L2 (per-rank KV stream "
                              f"{r['rank_bytes'] / 1e6:.0f} MB vs 126 MB)"},

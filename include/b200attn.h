@@ -271,6 +271,30 @@ int b200attn_paged_decode_ex(void* out, int64_t out_row_stride,
                              int max_context_len, int num_splits,
                              void* workspace, size_t workspace_bytes, void* stream);
 
+/* One decode step in one launch: b200attn_paged_decode_ex that first writes this step's K / V
+ * rows into the caches.  Replaces the pair the plugin issues per layer and step,
+ * tt.paged_update_cache for K and V followed by the paged decode op (attention.py:468-484,
+ * 634-668).  k_new / v_new: [num_users, num_kv_heads, head_size] bf16 rows, new_token_stride
+ * elements between users; user u's rows go to position cur_pos[u] with the addressing of
+ * b200attn_paged_update_cache (update_indices = cur_pos), converted for an fp8 cache.  The CTA
+ * that is about to stream the tile holding the new token writes it, fences, and then loads the
+ * tile, so no second kernel and no extra pass over the cache.  wrap_negative_positions != 0 keeps
+ * the reference's treatment of negative positions (torch floor division / negative column
+ * index, custom_ops.py:985-998); 0 skips such rows (the slot_mapping convention: -1 = padding).
+ * k_new == v_new == NULL makes it b200attn_paged_decode_ex. */
+int b200attn_paged_decode_step(void* out, int64_t out_row_stride,
+                               const void* q, int64_t q_row_stride,
+                               void* k_cache, void* v_cache,
+                               const void* k_new, const void* v_new, int64_t new_token_stride,
+                               int wrap_negative_positions,
+                               const int32_t* page_table, int64_t page_table_stride,
+                               int page_table_width, const int32_t* cur_pos,
+                               int num_users, int num_q_heads, int num_kv_heads, int head_size,
+                               int block_size, int64_t num_blocks, float scale,
+                               int sliding_window, const float* sinks, int cache_dtype,
+                               int max_context_len, int num_splits,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
 /* Split count the library would pick for a decode batch (host cost model fitted to B200
  * measurements; no device access beyond the SM count).  max_context_len <= 0 means "unknown": the page-table width bounds it. */
 int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,

@@ -64,6 +64,12 @@ SIGNATURES = {
          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p, c_int,
          c_int, c_int, c_void_p, c_size_t, c_void_p],
     ),
+    "b200attn_paged_decode_step": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+         c_int, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64,
+         c_float, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p],
+    ),
     "b200attn_paged_decode_static": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int,

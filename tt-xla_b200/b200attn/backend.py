@@ -383,14 +383,17 @@ class B200AttentionBackendImpl:
 
         inputs = self._prepare_inputs(query, key, value, attn_metadata)
         has_cache = kv_pair is not None
-        if has_cache and self.kv_sharing_target_layer_name is None:
-            self._handle_paged_attention(inputs, kv_pair, attn_metadata)
+        writes_cache = has_cache and self.kv_sharing_target_layer_name is None
         if inputs.is_prefill:
+            if writes_cache:
+                self._handle_paged_attention(inputs, kv_pair, attn_metadata)
             self._compute_full_attention(inputs, kv_pair, attn_metadata, output)
         else:
             if not has_cache:
                 raise ValueError("decode attention needs the paged KV cache")
-            self._compute_decode_attention(inputs, kv_pair, attn_metadata, output)
+            # the decode step's cache write (attention.py:468-484) rides in the decode launch
+            self._compute_decode_attention(inputs, kv_pair, attn_metadata, output,
+                                           write_new_token=writes_cache)
         return output
 
     @staticmethod
@@ -528,18 +531,23 @@ class B200AttentionBackendImpl:
             ops.prefill(q, k, v, cu_host, scale=self.scale, out=out, cu_q=cu_dev,
                         sliding_window=self._window)
 
-    def _compute_decode_attention(self, inputs, kv_pair, attn_metadata: B200Metadata, output) -> None:
-        """attention.py:634-668."""
+    def _compute_decode_attention(self, inputs, kv_pair, attn_metadata: B200Metadata, output,
+                                  write_new_token: bool = False) -> None:
+        """attention.py:634-668; with `write_new_token` also the K / V write of attention.py:468-484
+        (same positions, same page table) inside the same launch."""
         if attn_metadata.attn_mask is not None or not attn_metadata.is_causal:
             raise NotImplementedError("decode supports the causal cur_pos form only")
         users = inputs.users
+        fused = {}
+        if write_new_token:
+            fused = dict(new_key=inputs.key[:, 0], new_value=inputs.value[:, 0])
         ops.paged_decode(
             inputs.query.reshape(users, self.num_heads, self.head_size),
             kv_pair[0], kv_pair[1], attn_metadata.page_table, attn_metadata.cache_position,
             scale=self.scale,
             out=output.reshape(users, self.num_heads, self.head_size),
             max_context_len=attn_metadata.max_seq_len,
-            sliding_window=self._window, sinks=self._sinks_for(output.device),
+            sliding_window=self._window, sinks=self._sinks_for(output.device), **fused,
         )
 
     # ------------------------------------------------------------------ vLLM varlen form
@@ -552,17 +560,26 @@ class B200AttentionBackendImpl:
         n_tok = int(md.query_start_loc_cpu[-1])
         q = query[:n_tok].reshape(n_tok, nq, hd)
         out = output[:n_tok].reshape(n_tok, nq, hd)
-        if self.kv_sharing_target_layer_name is None:
+        nd = md.num_decodes
+        writes_cache = self.kv_sharing_target_layer_name is None
+        # A pure decode batch writes its new rows inside the decode launch (a row's slot is
+        # block_table[pos // bs] * bs + pos % bs, which is what that launch computes; padding
+        # rows carry position -1 and are skipped like slot -1); mixed batches scatter by slot.
+        fused = {}
+        if writes_cache and nd == n_tok and md.prefill_cu_q_cpu is None:
+            fused = dict(new_key=key[:n_tok].reshape(n_tok, nkv, hd),
+                         new_value=value[:n_tok].reshape(n_tok, nkv, hd),
+                         wrap_negative_positions=False)
+        elif writes_cache:
             ops.kv_scatter_slots(
                 kv_pair[0], kv_pair[1], key[:n_tok].reshape(n_tok, nkv, hd),
                 value[:n_tok].reshape(n_tok, nkv, hd), md.slot_mapping[:n_tok],
             )
-        nd = md.num_decodes
         if nd > 0:
             ops.paged_decode(
                 q[:nd], kv_pair[0], kv_pair[1], md.block_table[:nd], md.decode_cur_pos,
                 scale=self.scale, out=out[:nd], max_context_len=md.max_seq_len,
-                sliding_window=self._window, sinks=self._sinks_for(output.device),
+                sliding_window=self._window, sinks=self._sinks_for(output.device), **fused,
             )
         if md.prefill_cu_q_cpu is not None:
             assert self.sinks is None, "Attention sink is unsupported in SDPA prefill"

@@ -270,14 +270,21 @@ def paged_decode(
     workspace: Optional[torch.Tensor] = None,
     sliding_window: int = 0,
     sinks: Optional[torch.Tensor] = None,
+    new_key: Optional[torch.Tensor] = None,
+    new_value: Optional[torch.Tensor] = None,
+    wrap_negative_positions: bool = True,
 ) -> torch.Tensor:
     """Paged GQA decode attention: `tt.paged_scaled_dot_product_attention_decode` with
     is_causal=True and cur_pos_tensor (custom_ops.py:1198-1331).  `query`: [users, nq, hd]
     (or the reference's [1, users, nq, hd]); returns / fills `out` of the same shape.
     `sliding_window` > 0 limits each user to its last `sliding_window` keys; `sinks` (fp32
     [nq]) adds one denominator-only softmax column per head (the op's `sliding_window_size` /
-    `attention_sink` arguments, which the reference CPU branch ignores)."""
-    _need_cuda(query, k_cache, v_cache, page_table, cur_pos, out)
+    `attention_sink` arguments, which the reference CPU branch ignores).
+    With `new_key` / `new_value` ([users, nkv, hd] bf16) the same launch first writes those rows
+    into the caches at `cur_pos`, i.e. it is `paged_update_cache` + decode in one kernel;
+    `wrap_negative_positions=False` skips rows with a negative position instead of wrapping them
+    the way the reference's CPU indexing does."""
+    _need_cuda(query, k_cache, v_cache, page_table, cur_pos, out, new_key, new_value)
     nb, nkv, bs, hd = _check_cache(k_cache, v_cache)
     orig_shape = query.shape
     if query.dim() == 4:
@@ -317,11 +324,25 @@ def paged_decode(
         num_splits = L.b200attn_decode_auto_splits(users, nkv, hd, ctx)
     need = L.b200attn_decode_workspace_bytes(users, nq, hd, num_splits)
     ws = workspace if workspace is not None else _workspace(query.device, need)
+    kn = vn = None
+    nstride = 0
+    if (new_key is None) != (new_value is None):
+        raise ValueError("new_key and new_value go together")
+    if new_key is not None:
+        kn, nstride = _token_major(new_key, nkv, hd, "new_key")
+        vn, vstride = _token_major(new_value, nkv, hd, "new_value")
+        if kn.shape[0] != users or vn.shape[0] != users:
+            raise ValueError("new_key / new_value must hold one row per user")
+        if vstride != nstride:
+            kn, vn, nstride = kn.contiguous(), vn.contiguous(), nkv * hd
     _lib.check(
-        "b200attn_paged_decode_ex",
-        L.b200attn_paged_decode_ex(
+        "b200attn_paged_decode_step",
+        L.b200attn_paged_decode_step(
             out_t.data_ptr(), ostride, q.data_ptr(), qstride, k_cache.data_ptr(),
-            v_cache.data_ptr(), page_table.data_ptr(), page_table.stride(0), page_table.shape[1],
+            v_cache.data_ptr(), kn.data_ptr() if kn is not None else None,
+            vn.data_ptr() if vn is not None else None, nstride,
+            1 if wrap_negative_positions else 0,
+            page_table.data_ptr(), page_table.stride(0), page_table.shape[1],
             cur_pos.data_ptr(), users, nq, nkv, hd, bs, nb, float(scale), int(sliding_window),
             sinks.data_ptr() if sinks is not None else None, _cache_dtype(k_cache), max_context_len,
             num_splits, ws.data_ptr() if ws is not None else None,

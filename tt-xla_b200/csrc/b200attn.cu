@@ -559,6 +559,33 @@ int b200attn_paged_decode_ex(void* out, int64_t out_row_stride, const void* q,
                              const float* sinks, int cache_dtype, int max_context_len,
                              int num_splits, void* workspace, size_t workspace_bytes,
                              void* stream) {
+  return b200attn_paged_decode_step(out, out_row_stride, q, q_row_stride,
+                                    const_cast<void*>(k_cache), const_cast<void*>(v_cache),
+                                    nullptr, nullptr, 0, 1, page_table, page_table_stride,
+                                    page_table_width, cur_pos, num_users, num_q_heads, num_kv_heads,
+                                    head_size, block_size, num_blocks, scale, sliding_window, sinks,
+                                    cache_dtype, max_context_len, num_splits, workspace,
+                                    workspace_bytes, stream);
+}
+
+int b200attn_paged_decode_step(void* out, int64_t out_row_stride, const void* q,
+                               int64_t q_row_stride, void* k_cache, void* v_cache,
+                               const void* k_new, const void* v_new, int64_t new_token_stride,
+                               int wrap_negative_positions, const int32_t* page_table,
+                               int64_t page_table_stride, int page_table_width,
+                               const int32_t* cur_pos, int num_users, int num_q_heads,
+                               int num_kv_heads, int head_size, int block_size,
+                               int64_t num_blocks, float scale, int sliding_window,
+                               const float* sinks, int cache_dtype, int max_context_len,
+                               int num_splits, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  if ((k_new == nullptr) != (v_new == nullptr)) return B200ATTN_ERR_NULL_POINTER;
+  if (k_new) {
+    if (!aligned16(k_new) || !aligned16(v_new) || new_token_stride % 8 != 0)
+      return B200ATTN_ERR_MISALIGNED;
+    if (new_token_stride < static_cast<int64_t>(num_kv_heads) * head_size)
+      return B200ATTN_ERR_BAD_ARGUMENT;
+  }
   if (sliding_window < 0 || !(scale > 0.f)) return B200ATTN_ERR_BAD_ARGUMENT;
   if (cache_dtype != B200ATTN_CACHE_BF16 && cache_dtype != B200ATTN_CACHE_FP8_E4M3)
     return B200ATTN_ERR_BAD_ARGUMENT;
@@ -619,6 +646,13 @@ int b200attn_paged_decode_ex(void* out, int64_t out_row_stride, const void* q,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = sliding_window;
   p.sinks = sinks;
+  p.k_new = static_cast<const uint4*>(k_new);
+  p.v_new = static_cast<const uint4*>(v_new);
+  p.new_token_stride_v = new_token_stride / 8;
+  p.k_cache_w = static_cast<uint8_t*>(k_cache);
+  p.v_cache_w = static_cast<uint8_t*>(v_cache);
+  p.cache_fp8 = fp8 ? 1 : 0;
+  p.wrap_negative = wrap_negative_positions ? 1 : 0;
   p.err_word = dev->err_word;
   if (num_splits > 1) {
     const size_t rows_p = static_cast<size_t>(num_users) * num_q_heads * num_splits;

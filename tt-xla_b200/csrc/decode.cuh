@@ -11,6 +11,7 @@
 // warps' partial (m, l, O) are merged through shared memory at the end, and the CTA writes
 // either the final bf16 rows (one split) or an fp32 partial that the combine kernel merges.
 #pragma once
+#include "kv_scatter.cuh"
 #include "ptx.cuh"
 
 namespace b200attn {
@@ -38,8 +39,56 @@ struct DecodeParams {
   float scale_log2; // softmax scale * log2(e)
   int window;       // sliding window size in keys (0 = attend to the whole context)
   const float* sinks;  // [num_q_heads] attention-sink logits (scaled domain), or NULL
+  // Optional fused cache write of this step's K / V rows (the decode step's paged_update_cache):
+  const uint4* k_new;  // [users, nkv, hd] bf16 rows in 16-byte vectors, or NULL (no write)
+  const uint4* v_new;
+  int64_t new_token_stride_v;   // vectors between users
+  uint8_t* k_cache_w;  // cache bases as plain pointers for the write
+  uint8_t* v_cache_w;
+  int cache_fp8;       // 1: the caches hold e4m3
+  int wrap_negative;   // 1: a negative position wraps like the reference's CPU indexing, 0: skip
   int* err_word;
 };
+
+// The decode step's cache write, done by the one warp that is about to stream the tile holding
+// the new token: user u's K / V rows of KV head `kvh` go to position cur_pos[u], addressed
+// exactly as kv_scatter_kernel<kScatterUpdate> does (floor division, negative column wrap).
+// Every lane ends with a proxy fence so that the TMA loads issued afterwards by this warp read
+// the rows just written.
+template <int HD, int BS>
+__device__ __forceinline__ void decode_write_new_token(const DecodeParams& p, int user, int kvh,
+                                                       int lane) {
+  constexpr int kVec = HD / 8;   // 16-byte vectors of 8 values per row
+  const int pos = p.cur_pos[user];
+  if (pos < 0 && !p.wrap_negative) return;
+  int col = floordiv_i32(pos, BS);
+  const int off = pos - col * BS;
+  if (col < 0) col += p.page_table_width;
+  bool ok = col >= 0 && col < p.page_table_width;
+  int64_t blk = 0;
+  if (ok) {
+    blk = p.page_table[static_cast<int64_t>(user) * p.page_table_stride + col];
+    ok = blk >= 0 && blk < p.num_blocks;
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(p.err_word, kDevBadIndex);
+    return;
+  }
+  const int64_t row = (blk * p.num_kv_heads + kvh) * BS + off;
+  for (int i = lane; i < 2 * kVec; i += 32) {
+    const bool is_v = i >= kVec;
+    const int v = is_v ? i - kVec : i;
+    const uint4 val = __ldg((is_v ? p.v_new : p.k_new) +
+                            static_cast<int64_t>(user) * p.new_token_stride_v + kvh * kVec + v);
+    uint8_t* base = is_v ? p.v_cache_w : p.k_cache_w;
+    if (p.cache_fp8)
+      reinterpret_cast<uint2*>(base)[row * kVec + v] = bf16x8_to_e4m3x8(val);
+    else
+      reinterpret_cast<uint4*>(base)[row * kVec + v] = val;
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  __syncwarp();
+}
 
 // Folds an attention sink into a row's (max, sum): the sink is one more softmax column that
 // contributes to the denominator only.  Returns the factor the accumulated values scale by.
@@ -94,6 +143,9 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int G = p.group;
 
   if (t_begin >= t_end) {
+    // A row without context (negative position) still gets the reference's cache write.
+    if (p.k_new && n_tiles == 0 && split == 0 && warp == 0)
+      decode_write_new_token<HD, BS>(p, user, kvh, lane);
     // Nothing for this split: publish an empty partial (or zeros when it is the only split).
     if (p.num_splits > 1) {
       if (threadIdx.x < G) {
@@ -128,6 +180,8 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
       prefetch_tensormap(&tm_v);
     }
     const uint64_t policy = l2_policy_evict_first();
+    // the split that streams the last tile writes the new token's rows first
+    if (p.k_new && t_end == n_tiles) decode_write_new_token<HD, BS>(p, user, kvh, lane);
     const int n_pages = (ctx + BS - 1) / BS;
     const int32_t* pt = p.page_table + static_cast<int64_t>(user) * p.page_table_stride;
     const int first_page = t_begin * L::kPages;

@@ -96,6 +96,9 @@ paged_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int G = p.group;
 
   if (t_begin >= t_end) {
+    // A row without context (negative position) still gets the reference's cache write.
+    if (p.k_new && n_tiles == 0 && split == 0 && warp == 0)
+      decode_write_new_token<HD, BS>(p, user, kvh, lane);
     // Nothing for this split: publish an empty partial (or zeros when it is the only split).
     if (p.num_splits > 1) {
       if (threadIdx.x < G) {
@@ -130,6 +133,8 @@ paged_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_k,
       prefetch_tensormap(&tm_v);
     }
     const uint64_t policy = l2_policy_evict_first();
+    // the split that streams the last tile writes the new token's rows first
+    if (p.k_new && t_end == n_tiles) decode_write_new_token<HD, BS>(p, user, kvh, lane);
     const int n_pages = (ctx + BS - 1) / BS;
     const int32_t* pt = p.page_table + static_cast<int64_t>(user) * p.page_table_stride;
     int win_base = t_begin * L::kPages;
