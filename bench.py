@@ -545,8 +545,8 @@ def run_e2e_llama(args):
     rank = int(os.environ.get("RANK", "0"))
     if world > 1:
         os.environ["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"
-    if args.fused_linear:
-        os.environ["B200ATTN_FUSED_ROW_PARALLEL"] = "1"
+    # explicit either way, so that the line says what ran (the plugin's own default is "auto")
+    os.environ["B200ATTN_FUSED_ROW_PARALLEL"] = "1" if args.fused_linear else "0"
     from vllm import LLM, SamplingParams
 
     cfg_dir = tempfile.mkdtemp(prefix="llama31_8b_cfg_")

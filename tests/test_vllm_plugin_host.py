@@ -7,11 +7,12 @@ import torch
 vllm = pytest.importorskip("vllm")
 
 
-def test_register_points_custom_at_this_backend():
+def test_register_points_custom_at_this_backend(monkeypatch):
     from vllm.v1.attention.backends.registry import AttentionBackendEnum
 
     from b200attn import vllm_plugin
 
+    monkeypatch.setenv("B200ATTN_FUSED_ROW_PARALLEL", "0")     # keep vLLM's linear layers as they are
     vllm_plugin.register()
     assert AttentionBackendEnum.CUSTOM.get_path() == "b200attn.vllm_plugin.B200VllmAttentionBackend"
     B = vllm_plugin.B200VllmAttentionBackend
@@ -59,3 +60,21 @@ def test_fused_row_parallel_hook_is_idempotent_and_skips_single_rank_layers(monk
 
     with pytest.raises(AttributeError):
         hooked(types.SimpleNamespace(tp_size=1), torch.zeros(2, 8))
+
+
+def test_register_enables_the_row_parallel_hook_by_mode(monkeypatch):
+    """"auto" (the default) hooks groups of four ranks and more, "1" every tensor-parallel group,
+    "0" none."""
+    from b200attn import vllm_plugin
+
+    seen = []
+    monkeypatch.setattr(vllm_plugin, "enable_fused_row_parallel", lambda **kw: seen.append(kw))
+    for mode, want in (("0", []), ("1", [dict(min_world=2)]), ("auto", [dict(min_world=4)]),
+                       (None, [dict(min_world=4)])):
+        seen.clear()
+        if mode is None:
+            monkeypatch.delenv("B200ATTN_FUSED_ROW_PARALLEL", raising=False)
+        else:
+            monkeypatch.setenv("B200ATTN_FUSED_ROW_PARALLEL", mode)
+        vllm_plugin.register()
+        assert seen == want, mode

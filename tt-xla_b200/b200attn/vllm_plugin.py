@@ -106,18 +106,22 @@ def register() -> None:
 
     register_backend(AttentionBackendEnum.CUSTOM,
                      "b200attn.vllm_plugin.B200VllmAttentionBackend")
-    if os.environ.get("B200ATTN_FUSED_ROW_PARALLEL", "0") == "1":
-        enable_fused_row_parallel()
+    # o_proj / down_proj through the fused GEMM + all-reduce launch: "1" for every tensor-parallel
+    # size, "0" never, "auto" (default) from four ranks up, where it measured faster end to end
+    # than vLLM's GEMM + all-reduce (two ranks: a tie).
+    mode = os.environ.get("B200ATTN_FUSED_ROW_PARALLEL", "auto")
+    if mode in ("1", "auto"):
+        enable_fused_row_parallel(min_world=2 if mode == "1" else 4)
 
 
-def enable_fused_row_parallel(max_tokens: int = 128, max_n: int = 8192) -> None:
+def enable_fused_row_parallel(max_tokens: int = 128, max_n: int = 8192, min_world: int = 2) -> None:
     """Points vLLM's RowParallelLinear (o_proj, down_proj: the layers the reference row-shards,
     vllm_tt/vllm_distributed_utils.py:356-363) at the fused GEMM + all-reduce launch for bf16
     batches of up to `max_tokens` rows; every other case keeps vLLM's GEMM + all-reduce.
 
     The communicator of the tensor-parallel group is created at the first forward of any such
     layer, which all ranks reach together during vLLM's eager profiling pass, well before decode
-    steps are captured into CUDA graphs.  Off unless B200ATTN_FUSED_ROW_PARALLEL=1."""
+    steps are captured into CUDA graphs.  Layers of groups smaller than `min_world` are left alone."""
     import torch
     from vllm.distributed import get_tp_group
     from vllm.model_executor.layers.linear import RowParallelLinear, UnquantizedLinearMethod
@@ -131,7 +135,7 @@ def enable_fused_row_parallel(max_tokens: int = 128, max_n: int = 8192) -> None:
 
     def forward(self, input_):
         eligible = (
-            self.tp_size > 1 and self.reduce_results and self.input_is_parallel
+            self.tp_size >= min_world and self.reduce_results and self.input_is_parallel
             and self.bias is None and isinstance(self.quant_method, UnquantizedLinearMethod)
             and input_.dim() == 2 and input_.dtype == torch.bfloat16 and input_.is_cuda
             and self.weight.dtype == torch.bfloat16 and self.weight.shape[0] <= max_n
