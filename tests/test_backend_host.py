@@ -67,15 +67,14 @@ def test_impl_constructor_errors():
 def test_normalize_shapes_and_messages():
     impl = B200AttentionBackendImpl(8, 64, 0.125, 2, None, None, "auto")
     x = torch.zeros(6, 8 * 64)
-    assert impl._normalize_to_attention_format(x, "query", 8, 64, 3).shape == (3, 2, 8, 64)
-    assert impl._normalize_to_attention_format(x.view(6, 8, 64), "query", 8, 64, 2).shape == \
-        (2, 3, 8, 64)
+    assert backend.rows_by_user(x, "query", 8, 64, 3).shape == (3, 2, 8, 64)
+    assert backend.rows_by_user(x.view(6, 8, 64), "query", 8, 64, 2).shape == (2, 3, 8, 64)
     with pytest.raises(ValueError, match="rank >= 2"):
-        impl._normalize_to_attention_format(torch.zeros(5), "query", 8, 64, 1)
+        backend.rows_by_user(torch.zeros(5), "query", 8, 64, 1)
     with pytest.raises(ValueError, match="flattened-token tensor"):
-        impl._normalize_to_attention_format(torch.zeros(6, 100), "key", 2, 64, 3)
+        backend.rows_by_user(torch.zeros(6, 100), "key", 2, 64, 3)
     with pytest.raises(ValueError, match="divisible"):
-        impl._normalize_to_attention_format(x, "query", 8, 64, 4)
+        backend.rows_by_user(x, "query", 8, 64, 4)
     md = B200Metadata(num_users=3)
     ins = impl._prepare_inputs(x, torch.zeros(6, 2 * 64), torch.zeros(6, 2 * 64), md)
     assert ins.is_prefill and ins.query_num_tokens == 2 and ins.users == 3

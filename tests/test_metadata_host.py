@@ -32,15 +32,6 @@ def test_same_block_run():
     assert len(set(starts.tolist())) == 1
 
 
-def test_token_paddings():
-    assert md.get_token_paddings(32, 512) == [1, 32, 64, 128, 256, 512]
-    assert md.get_token_paddings(20, 100) == [1, 32, 64, 128]
-    assert md.get_token_paddings(48, 64) == [1, 64]
-    p = md.get_token_paddings(32, 512)
-    assert md.get_padded_token_len(p, 1) == 1 and md.get_padded_token_len(p, 33) == 64
-    assert md.adjust_min_token(64) == 64 and md.adjust_min_token(100) == 128
-
-
 def test_fill_page_table_width():
     # the step's token budget in blocks, rounded to 8 entries, capped at the read width
     assert md.fill_page_table_width(512, 32, 2048) == 16

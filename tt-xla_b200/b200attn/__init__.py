@@ -7,6 +7,7 @@ CUDA device is missing.
 """
 from . import _lib, ops  # noqa: F401
 from .backend import (  # noqa: F401
+    B200Attention,
     B200AttentionBackend,
     B200AttentionBackendImpl,
     B200AttentionMetadataBuilder,
@@ -15,6 +16,7 @@ from .backend import (  # noqa: F401
 
 __all__ = [
     "ops",
+    "B200Attention",
     "B200AttentionBackend",
     "B200AttentionBackendImpl",
     "B200AttentionMetadataBuilder",

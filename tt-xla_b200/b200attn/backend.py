@@ -18,7 +18,6 @@ Two metadata forms reach `forward`:
 """
 from __future__ import annotations
 
-from collections import namedtuple
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -226,18 +225,20 @@ class B200AttentionBackend:
     def swap_blocks(src_kv_cache, dst_kv_cache, src_to_dst) -> None:
         raise RuntimeError("swap_blocks is not used for the B200 backend.")
 
-    @staticmethod
-    def get_min_page_size(max_model_len: int, max_num_seqs: int) -> int:
-        # attention.py:126-135 (page-table bytes kept under half a MiB), as plain arithmetic.
-        max_num_page_per_req = 1024 * 1024 // 2 // max_num_seqs // 4
-        min_page_size = cdiv(max_model_len, max_num_page_per_req)
-        return 1 << (min_page_size - 1).bit_length()
+    # The plugin keeps one request's page-table row under a fixed budget of int32 entries:
+    # 128 Ki entries (half a MiB) shared by all resident requests (attention.py:126-140).
+    PAGE_TABLE_ENTRY_BUDGET = (1 << 20) // 2 // 4
 
-    @staticmethod
-    def get_max_num_seqs(model_len: int, page_size: int) -> int:
-        # attention.py:137-140.
-        num_page_per_req = cdiv(model_len, page_size)
-        return 1024 * 1024 // 2 // num_page_per_req // 4
+    @classmethod
+    def get_min_page_size(cls, max_model_len: int, max_num_seqs: int) -> int:
+        """Smallest power-of-two page size whose page-table rows fit the entry budget."""
+        entries_per_request = cls.PAGE_TABLE_ENTRY_BUDGET // max_num_seqs
+        return 1 << (cdiv(max_model_len, entries_per_request) - 1).bit_length()
+
+    @classmethod
+    def get_max_num_seqs(cls, model_len: int, page_size: int) -> int:
+        """How many requests of `model_len` tokens fit the entry budget at `page_size`."""
+        return cls.PAGE_TABLE_ENTRY_BUDGET // cdiv(model_len, page_size)
 
     @staticmethod
     def get_page_size(vllm_config=None) -> int:
@@ -254,41 +255,74 @@ class B200AttentionBackend:
 
 
 def dtype_bits(dtype: torch.dtype) -> int:
-    """attention.py:721-737."""
-    if dtype.is_floating_point:
-        return torch.finfo(dtype).bits
+    """Storage bits of one element (attention.py:721-737); bool counts as a byte."""
     if dtype == torch.bool:
         return 8
-    return torch.iinfo(dtype).bits
+    info = torch.finfo(dtype) if dtype.is_floating_point else torch.iinfo(dtype)
+    return info.bits
 
 
 def get_dtype_packing(dtype: torch.dtype) -> int:
-    """attention.py:740-747: elements per 32-bit word."""
+    """Elements per 32-bit word (attention.py:740-747)."""
     bits = dtype_bits(dtype)
-    if 32 % bits != 0:
+    per_word, rest = divmod(32, bits)
+    if rest:
         raise ValueError(f"The bit width must be divisible by 32, but got bits={bits}")
-    return 32 // bits
+    return per_word
 
 
 def get_page_size_bytes(
     block_size: int, num_kv_heads: int, head_size: int, kv_cache_dtype: torch.dtype
 ) -> int:
-    """attention.py:750-771: bytes of one page holding K and V, head_size padded to 32."""
-    padded_head_size = cdiv(head_size, HEAD_SIZE_ALIGNMENT) * HEAD_SIZE_ALIGNMENT
-    num_combined_kv_heads = num_kv_heads * 2
+    """Bytes of one page holding K and V (attention.py:750-771): head_size rounded up to the
+    device's 32-element granule, the 2 * num_kv_heads rows rounded up to whole 32-bit words."""
     packing = get_dtype_packing(kv_cache_dtype)
-    num_combined_kv_heads = cdiv(num_combined_kv_heads, packing) * packing
-    kv_cache_dtype_bits = dtype_bits(kv_cache_dtype)
-    return block_size * num_combined_kv_heads * padded_head_size * kv_cache_dtype_bits // 8
+    rows = cdiv(2 * num_kv_heads, packing) * packing
+    width = cdiv(head_size, HEAD_SIZE_ALIGNMENT) * HEAD_SIZE_ALIGNMENT
+    return block_size * rows * width * dtype_bits(kv_cache_dtype) // 8
 
 
-AttentionInputs = namedtuple(
-    "AttentionInputs",
-    [
-        "query", "key", "value", "orig_query_shape", "orig_query_ndim", "users",
-        "query_num_tokens", "is_prefill", "users_kv", "kv_num_tokens",
-    ],
-)
+def rows_by_user(tensor: torch.Tensor, name: str, heads: int, head_size: int,
+                 users: int) -> torch.Tensor:
+    """View of a plugin-form activation as [users, tokens, heads, head_size].  Accepted inputs
+    and the error texts are those of attention.py:338-379: token rows flattened to
+    `heads * head_size` columns, or already split into (heads, head_size)."""
+    hidden = heads * head_size
+    if tensor.ndim < 2:
+        raise ValueError(f"{name} must have rank >= 2, got shape={tuple(tensor.shape)}")
+    flat = tensor.ndim == 2 and tensor.shape[1] == hidden
+    split = tensor.ndim == 3 and tuple(tensor.shape[1:]) == (heads, head_size)
+    if not (flat or split):
+        raise ValueError(
+            f"{name} must be either a flattened-token tensor with "
+            f"shape[-1] == {hidden} or a head-shaped tensor with "
+            f"shape[-2:] == ({heads}, {head_size}); "
+            f"got shape={tuple(tensor.shape)}"
+        )
+    rows = tensor.shape[0]
+    if rows % users:
+        raise ValueError(
+            f"{name} total tokens ({rows}) must be divisible "
+            f"by num_users ({users})"
+        )
+    return tensor.reshape(users, rows // users, heads, head_size)
+
+
+@dataclass
+class PluginBatch:
+    """One pass in the plugin's [users x tokens] form.  The whole batch is in one mode: a pass
+    with more than one query token per user is a prefill pass (attention.py:429)."""
+
+    query: torch.Tensor      # [users, tokens, nq, hd]
+    key: torch.Tensor        # [users, tokens, nkv, hd]
+    value: torch.Tensor
+    users: int
+    query_num_tokens: int
+    kv_num_tokens: int
+
+    @property
+    def is_prefill(self) -> bool:
+        return self.query_num_tokens > 1
 
 
 class B200AttentionBackendImpl:
@@ -408,66 +442,19 @@ class B200AttentionBackendImpl:
             return kv_cache[0], kv_cache[1]
         return None
 
-    def _normalize_to_attention_format(
-        self, tensor: torch.Tensor, tensor_name: str, expected_num_heads: int,
-        expected_head_size: int, num_users: int,
-    ) -> torch.Tensor:
-        """[users, tokens, heads, head_size] view; same acceptance rules and messages as
-        attention.py:338-379."""
-        if tensor.ndim < 2:
-            raise ValueError(
-                f"{tensor_name} must have rank >= 2, got shape={tuple(tensor.shape)}"
-            )
-        expected_hidden = expected_num_heads * expected_head_size
-        if tensor.ndim == 2 and tensor.shape[-1] == expected_hidden:
-            normalized = tensor.reshape(-1, expected_num_heads, expected_head_size)
-        elif (
-            tensor.ndim == 3
-            and tensor.shape[-2] == expected_num_heads
-            and tensor.shape[-1] == expected_head_size
-        ):
-            normalized = tensor
-        else:
-            raise ValueError(
-                f"{tensor_name} must be either a flattened-token tensor with "
-                f"shape[-1] == {expected_hidden} or a head-shaped tensor with "
-                f"shape[-2:] == ({expected_num_heads}, {expected_head_size}); "
-                f"got shape={tuple(tensor.shape)}"
-            )
-        total_tokens = normalized.shape[0]
-        if total_tokens % num_users != 0:
-            raise ValueError(
-                f"{tensor_name} total tokens ({total_tokens}) must be divisible "
-                f"by num_users ({num_users})"
-            )
-        return normalized.reshape(num_users, -1, expected_num_heads, expected_head_size)
-
-    def _prepare_inputs(self, query, key, value, attn_metadata: B200Metadata) -> AttentionInputs:
-        """attention.py:381-459."""
-        num_users = attn_metadata.num_users
-        assert num_users is not None, "num_users must be provided in attn_metadata."
-        orig_query_shape, orig_query_ndim = query.shape, query.ndim
-        query = self._normalize_to_attention_format(
-            query, "query", self.num_heads, self.head_size, num_users
-        )
-        key = self._normalize_to_attention_format(
-            key, "key", self.num_kv_heads, self.head_size, num_users
-        )
-        value = self._normalize_to_attention_format(
-            value, "value", self.num_kv_heads, self.head_size, num_users
-        )
-        if key.shape != value.shape:
+    def _prepare_inputs(self, query, key, value, attn_metadata: B200Metadata) -> PluginBatch:
+        """Shapes the three activations by user (what attention.py:381-459 hands its ops)."""
+        users = attn_metadata.num_users
+        assert users is not None, "num_users must be provided in attn_metadata."
+        q = rows_by_user(query, "query", self.num_heads, self.head_size, users)
+        k = rows_by_user(key, "key", self.num_kv_heads, self.head_size, users)
+        v = rows_by_user(value, "value", self.num_kv_heads, self.head_size, users)
+        if k.shape != v.shape:
             raise ValueError(
                 f"key and value must match after normalization, got "
-                f"key={tuple(key.shape)} value={tuple(value.shape)}"
+                f"key={tuple(k.shape)} value={tuple(v.shape)}"
             )
-        query_num_tokens = query.shape[1]
-        return AttentionInputs(
-            query=query, key=key, value=value, orig_query_shape=orig_query_shape,
-            orig_query_ndim=orig_query_ndim, users=num_users,
-            query_num_tokens=query_num_tokens, is_prefill=query_num_tokens > 1,
-            users_kv=key.shape[0], kv_num_tokens=key.shape[1],
-        )
+        return PluginBatch(q, k, v, users, q.shape[1], k.shape[1])
 
     def _handle_paged_attention(self, inputs, kv_pair, attn_metadata: B200Metadata) -> None:
         """KV-cache write (attention.py:461-515): one launch covers K and V."""
@@ -588,6 +575,73 @@ class B200AttentionBackendImpl:
                 page_table=md.block_table[nd:], q_start=md.prefill_q_start, out=out[nd:],
                 cu_q=md.prefill_cu_q, sliding_window=self._window,
             )
+
+
+def flatten_heads(tensor: Optional[torch.Tensor], name: str, heads: int,
+                  head_size: int) -> Optional[torch.Tensor]:
+    """Any-rank activation -> [rows, heads * head_size] (the layer wrapper's input rule,
+    attention.py:798-825): the last dim is already the hidden width, or the last two are
+    (heads, head_size)."""
+    if tensor is None:
+        return None
+    if tensor.ndim < 2:
+        raise ValueError(f"{name} must have rank >= 2, got shape={tuple(tensor.shape)}")
+    hidden = heads * head_size
+    if tensor.shape[-1] != hidden and tuple(tensor.shape[-2:]) != (heads, head_size):
+        raise ValueError(
+            f"{name} must satisfy one of: "
+            f"shape[-1] == {hidden} or "
+            f"shape[-2:] == ({heads}, {head_size}); "
+            f"got shape={tuple(tensor.shape)}"
+        )
+    return tensor.reshape(-1, hidden)
+
+
+class B200Attention(torch.nn.Module):
+    """Attention layer around the backend Impl for callers outside vLLM, with the input handling
+    of the plugin's `TTAttention` wrapper (attention.py:774-856): query / key / value of any rank
+    are flattened to 2-D token rows, the Impl runs, and the result comes back in the query's
+    shape.  The layer owns what vLLM's `Attention` would hold for it: the Impl, the bound
+    `kv_cache` pair (see `sharding.allocate_kv_caches` / `bind_kv_caches`) and the step's
+    metadata (`set_metadata`, or the `attn_metadata` argument)."""
+
+    def __init__(self, num_heads: int, head_size: int, scale: float,
+                 num_kv_heads: Optional[int] = None, **impl_kwargs) -> None:
+        super().__init__()
+        self.num_heads = num_heads
+        self.head_size = self.head_size_v = head_size
+        self.num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
+        self.impl = B200AttentionBackendImpl(
+            num_heads, head_size, scale, self.num_kv_heads,
+            impl_kwargs.pop("alibi_slopes", None), impl_kwargs.pop("sliding_window", None),
+            impl_kwargs.pop("kv_cache_dtype", "auto"), impl_kwargs.pop("logits_soft_cap", None),
+            impl_kwargs.pop("attn_type", DECODER),
+            impl_kwargs.pop("kv_sharing_target_layer_name", None), impl_kwargs.pop("sinks", None))
+        if impl_kwargs:
+            raise TypeError(f"unexpected arguments: {sorted(impl_kwargs)}")
+        self.kv_cache = None
+        self.attn_metadata: Optional[B200Metadata] = None
+
+    def set_metadata(self, attn_metadata: B200Metadata) -> None:
+        self.attn_metadata = attn_metadata
+
+    def forward(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                output_shape: Optional[torch.Size] = None,
+                attn_metadata: Optional[B200Metadata] = None) -> torch.Tensor:
+        q2 = flatten_heads(query, "query", self.num_heads, self.head_size)
+        k2 = flatten_heads(key, "key", self.num_kv_heads, self.head_size)
+        v2 = flatten_heads(value, "value", self.num_kv_heads, self.head_size_v)
+        out = torch.empty(output_shape if output_shape is not None else q2.shape,
+                          dtype=q2.dtype, device=q2.device)
+        md = attn_metadata if attn_metadata is not None else self.attn_metadata
+        self.impl.forward(self, q2, k2, v2, self.kv_cache, md, output=out.view(q2.shape[0], -1))
+        if out.numel() != query.numel():
+            raise ValueError(
+                "Cannot reshape attention output back to query shape: "
+                f"output_shape={tuple(out.shape)}, "
+                f"query_shape={tuple(query.shape)}"
+            )
+        return out.reshape(query.shape)
 
 
 def write_to_kv_cache(key, value, kv_cache, slot_mapping, *unused, **unused_kw) -> None:

@@ -9,12 +9,11 @@ attention path receives:
     fill_page_table[i] = roll(page_table[i], -num_computed_i // block_size), narrowed to
         the step's width                                          (:1955-1993, :1255-1286)
     chunk_start_idx = the one shared num_computed - row_lead      (:1863-1887)
-    _row_lead / _same_block_run / _get_token_paddings / _get_padded_token_len (:5201-5340)
+    _row_lead / _same_block_run                                  (:5284-5307)
 and the slot addressing the live path implies (slot = page_table[u, p // bs] * bs + p % bs).
 """
 from __future__ import annotations
 
-import bisect
 from dataclasses import dataclass
 from typing import Optional
 
@@ -42,33 +41,6 @@ def same_block_run(num_computed: np.ndarray, block_size: int) -> int:
     boundary = num_computed // block_size
     differs = np.flatnonzero(boundary != boundary[0])
     return int(differs[0]) if differs.size else int(num_computed.size)
-
-
-def adjust_min_token(min_token_size: int) -> int:
-    """Power of two, at least 32 (model_runner.py:5201-5223)."""
-    if (min_token_size & (min_token_size - 1)) == 0 and min_token_size >= 32:
-        return min_token_size
-    return 32 if min_token_size <= 32 else 1 << (min_token_size - 1).bit_length()
-
-
-def get_token_paddings(min_token_size: int, max_token_size: int) -> list[int]:
-    """[1, m, 2m, 4m, ...] up to the first value covering max_token_size
-    (model_runner.py:5225-5245)."""
-    num = adjust_min_token(min_token_size)
-    paddings = [1]
-    while True:
-        paddings.append(num)
-        if num >= max_token_size:
-            break
-        num *= 2
-    return paddings
-
-
-def get_padded_token_len(paddings: list[int], x: int) -> int:
-    """First padding >= x (model_runner.py:5248-5252)."""
-    index = bisect.bisect_left(paddings, x)
-    assert index < len(paddings)
-    return paddings[index]
 
 
 def fill_page_table_width(max_num_tokens: int, block_size: int, read_width: int) -> int:

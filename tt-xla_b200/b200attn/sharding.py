@@ -87,3 +87,66 @@ def gather_heads(parts: list[torch.Tensor], head_size: int) -> torch.Tensor:
     """Concatenates per-rank outputs [tokens, nq/g*hd] back into [tokens, nq*hd] (rank order)."""
     tokens = parts[0].shape[0]
     return torch.cat([p.reshape(tokens, -1, head_size) for p in parts], dim=1).reshape(tokens, -1)
+
+
+def allocate_kv_caches(
+    layer_names,
+    num_blocks: int,
+    num_kv_heads: int,
+    block_size: int,
+    head_size: int,
+    *,
+    dtype: torch.dtype = torch.bfloat16,
+    device=None,
+    tp_size: int = 1,
+    shared_kv_layers=None,
+) -> dict:
+    """Per-layer paged caches the way the plugin's runner creates them
+    (`initialize_kv_cache`, model_runner.py:4560-4630): for every attention layer a zeroed
+    `[k_cache, v_cache]` pair of `B200AttentionBackend.get_kv_cache_shape`, separate tensors so a
+    decode step never slices or concatenates.  Under tensor parallelism each rank allocates only
+    its own KV heads — a dense `[num_blocks, num_kv_heads / tp_size, block_size, head_size]`
+    tensor, the per-device shard of the reference's `(None, "model", None, None)` sharding
+    (:4632-4656) — after the same divisibility check (:4590-4599).
+
+    `layer_names`: names, or a layer count (names become "layers.<i>.attn").
+    `shared_kv_layers`: {layer: target layer} for cross-layer KV sharing; such a layer gets the
+    target's pair itself, not a copy (`maybe_setup_cross_layer_kv_sharing`).
+    Returns {layer name: [k_cache, v_cache]} in layer order."""
+    from .backend import B200AttentionBackend
+
+    if isinstance(layer_names, int):
+        layer_names = [f"layers.{i}.attn" for i in range(layer_names)]
+    if tp_size > 1:
+        assert num_kv_heads % tp_size == 0, (
+            f"num_kv_heads {num_kv_heads} must be divisible by tp_size {tp_size} "
+            "for correct KV-head sharding"
+        )
+    if not B200AttentionBackend.supports_head_size(head_size):
+        raise ValueError(f"head_size {head_size} is not supported (64 or 128)")
+    if not B200AttentionBackend.supports_block_size(block_size):
+        raise ValueError(f"block_size {block_size} is not supported (32 or 64)")
+    if dtype not in (torch.bfloat16, torch.float8_e4m3fn):
+        raise ValueError("KV caches are bfloat16 or float8_e4m3fn")
+    shared_kv_layers = dict(shared_kv_layers or {})
+    shape = B200AttentionBackend.get_kv_cache_shape(
+        num_blocks, block_size, num_kv_heads // max(tp_size, 1), head_size)
+    caches: dict = {}
+    for name in layer_names:
+        if name in shared_kv_layers:
+            continue
+        caches[name] = [torch.zeros(shape, dtype=dtype, device=device),
+                        torch.zeros(shape, dtype=dtype, device=device)]
+    for name, target in shared_kv_layers.items():
+        if target not in caches:
+            raise ValueError(f"layer {name} shares the KV cache of unknown layer {target}")
+        caches[name] = caches[target]
+    return {name: caches[name] for name in layer_names}
+
+
+def bind_kv_caches(layers: dict, caches: dict) -> None:
+    """Hands every attention layer its cache pair (`bind_kv_cache`, model_runner.py:4626-4630):
+    sets `layer.kv_cache` for each name present in both mappings."""
+    for name, layer in layers.items():
+        if name in caches:
+            layer.kv_cache = caches[name]

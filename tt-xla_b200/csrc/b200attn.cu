@@ -19,7 +19,8 @@
 
 namespace b200attn {
 
-__device__ int g_err_word = 0;
+// Diagnostics block: code, pad, globaltimer stamp of the latest timeout (see ptx.cuh).
+__device__ __align__(16) int g_err_word[4] = {0, 0, 0, 0};
 
 // Split-KV scratch of b200attn_paged_decode_static.  In host code this name is only a handle
 // for cudaGetSymbolAddress; kernels get the device address looked up below.
@@ -265,15 +266,20 @@ static int launch_rowlinear(const CUtensorMap& tw, const CUtensorMap& tx, const 
   static int max_clusters[kMaxDevices] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (max_clusters[dev] == 0) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
-      cudaGetLastError();
-      return B200ATTN_ERR_UNSUPPORTED;
+  int resident = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (max_clusters[dev] == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_UNSUPPORTED;
+      }
+      max_clusters[dev] = n > 0 ? n : -1;
     }
-    max_clusters[dev] = n > 0 ? n : -1;
+    resident = max_clusters[dev];
   }
-  if (max_clusters[dev] < tiles) return B200ATTN_ERR_TOO_LARGE;
+  if (resident < tiles) return B200ATTN_ERR_TOO_LARGE;
   e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   return static_cast<int>(e);
 }
@@ -726,7 +732,8 @@ int b200attn_prefill_ex(void* out, int64_t out_row_stride, const void* q, int64_
     if (len < 0) return B200ATTN_ERR_BAD_ARGUMENT;
     total_tiles += (len + kPfRowsPerItem - 1) / kPfRowsPerItem;
   }
-  if (cu_q_host[num_seqs] - cu_q_host[0] > total_q) return B200ATTN_ERR_BAD_ARGUMENT;
+  // rows are addressed absolutely (cu_q[s] + row), so the offsets must start at 0 and end inside q
+  if (cu_q_host[0] != 0 || cu_q_host[num_seqs] > total_q) return B200ATTN_ERR_BAD_ARGUMENT;
   if (total_tiles == 0) return B200ATTN_OK;
   if (static_cast<int64_t>(total_tiles) * num_q_heads > 0x7fffffffLL) return B200ATTN_ERR_TOO_LARGE;
 

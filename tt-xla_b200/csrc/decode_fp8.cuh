@@ -77,8 +77,8 @@ paged_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_k,
   uint64_t* empty_bar = full_bar + STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + STAGES);
 
-  // A CTA of this launch already gave up on a wait: do not repeat the timeout per CTA.
-  if (*reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout) return;
+  // A CTA of this launch just gave up on a wait: do not repeat the timeout per CTA.
+  if (timeout_drain_window(p.err_word)) return;
 
   const int split = blockIdx.x;
   const int kvh = blockIdx.y;

@@ -218,8 +218,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // A CTA of this launch already gave up on a wait: do not repeat the timeout per CTA.
-  if (*reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout) return;
+  // A CTA of this launch just gave up on a wait: do not repeat the timeout per CTA.
+  if (timeout_drain_window(p.err_word)) return;
 
   const bool cu_cached = p.num_seqs <= kPfSeqCache;
   if (cu_cached)

@@ -16,6 +16,31 @@ constexpr int kDevBadIndex = 2;
 // A wait gives up after this much wall time (globaltimer nanoseconds).  A healthy pipeline
 // completes a wait in microseconds; the bound only matters for a broken one.
 constexpr uint64_t kWaitTimeoutNs = 200ull * 1000 * 1000;
+// After a timeout, CTAs that start within this window return at once (see timeout_drain_window).
+constexpr uint64_t kTimeoutDrainNs = 1000ull * 1000 * 1000;
+
+// The diagnostics block is four 32-bit words: [0] the code the host reads and clears, [1] unused,
+// [2..3] the globaltimer value of the latest timeout.
+__device__ __forceinline__ void report_wait_timeout(int* err_word) {
+  *reinterpret_cast<volatile uint64_t*>(err_word + 2) = 0;   // placeholder until the stamp below
+  uint64_t now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  *reinterpret_cast<volatile uint64_t*>(err_word + 2) = now;
+  __threadfence();
+  atomicExch(err_word, kDevWaitTimeout);
+}
+
+// True while the launch in which a wait ran out is still draining: its remaining CTAs (and any
+// launch queued right behind it) skip their work instead of each waiting out the same timeout.
+// The window closes by itself, so later launches run normally even if the host never reads the
+// word; the word itself stays set until the host reads it.
+__device__ __forceinline__ bool timeout_drain_window(const int* err_word) {
+  if (*reinterpret_cast<const volatile int*>(err_word) != kDevWaitTimeout) return false;
+  const uint64_t stamp = *reinterpret_cast<const volatile uint64_t*>(err_word + 2);
+  uint64_t now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  return now - stamp < kTimeoutDrainNs;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -89,7 +114,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     }
   }
   *abort_flag = 1;
-  atomicExch(err_word, kDevWaitTimeout);
+  report_wait_timeout(err_word);
   return false;
 }
 

@@ -54,6 +54,9 @@ constexpr size_t kRlStageOff = 32768;   // staging starts here; the header sits 
 struct RowLinearComm {       // the first bytes of a communicator buffer
   uint32_t epoch;            // calls completed on this rank
   uint32_t ticket;           // CTAs of the running call that have finished
+  uint32_t out_of_step;      // a wait for a peer ran out on this rank: the ranks no longer agree
+                             // on the epoch, and every later call through this communicator only
+                             // runs its GEMM; a new communicator starts clean
 };
 
 struct RowLinearParams {
@@ -262,9 +265,10 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     // Everything below reads or writes memory other kernels touch: wait for them first.
     grid_dependency_wait();
     if (et == 0) {
-      // A wait of an earlier launch ran out: the ranks are no longer in step.  The GEMM still
-      // runs (its loads are already on their way), but nothing is published or waited for.
-      *dead_slot = *reinterpret_cast<volatile int*>(p.err_word) == kDevWaitTimeout;
+      // A wait of an earlier call through this communicator ran out: the ranks are no longer
+      // in step.  The GEMM still runs (its loads are already on their way), but nothing is
+      // published or waited for.
+      *dead_slot = p.world > 1 && *reinterpret_cast<volatile uint32_t*>(&hdr->out_of_step) != 0u;
       *epoch_slot = p.world > 1 ? *reinterpret_cast<volatile uint32_t*>(&hdr->epoch) + 1u : 1u;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -392,7 +396,8 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
               t0 = now;
             } else if (now - t0 > p.peer_timeout_ns) {
               *abort_flag = 1;
-              atomicExch(p.err_word, kDevWaitTimeout);
+              *reinterpret_cast<volatile uint32_t*>(&hdr->out_of_step) = 1u;
+              report_wait_timeout(p.err_word);
               gave_up = true;
               break;
             }
