@@ -6,17 +6,21 @@
 Default workload ("c4"): long-context paged GQA decode with Llama-3.1-70B attention shapes
 (64 q heads, 8 kv heads, head_dim 128, bf16, batch 32, every context 32768 tokens, block 64),
 KV heads sharded across the N GPUs with no data-path collective.  One step = one decode pass of
-the hot path over the batch: the KV write of the new token, done inside the split-KV decode
-launch, and the split combine (2 launches; 1 when the batch needs no split).  The headline value is decode-attention HBM GB/s: algorithmic bytes of
-the batch divided by the step time (max over ranks).
+the hot path over the batch, ONE launch: the split-KV decode kernel writes the new token's K/V
+rows, streams the cache and merges its splits.  The headline value is decode-attention HBM GB/s:
+algorithmic bytes of the batch divided by the step time (max over ranks).
 
 One JSON line is printed by rank 0.  Besides the contract keys it carries
-  roofline      the decode call (split-KV kernel + combine) against the measured HBM peak,
+  roofline      the decode launch against the measured HBM peak,
   cpu_baseline  the CPU oracle port timed on a bounded sample on this machine's cores (N=1),
   e2e           the same metric through B200AttentionBackendImpl.forward with pinned HOST inputs
                 copied in and the output copied back every step (the KV cache is the runner's
                 resident state, as in the plugin),
-  prefill       the config-2 causal prefill (tcgen05 kernel) in TFLOP/s against the tensor peak.
+  parity_check  the timed step's output rows of two users against the CPU oracle,
+  sustained     the same step replayed for about two seconds (median and spread),
+  prefill       the config-2 causal prefill (tcgen05 kernel) in TFLOP/s against the tensor peak,
+  extra_workloads  configs 1 and 3 (decode rows), and for N > 1 the row-parallel linear,
+  e2e_model     config 5: Llama-3.1-8B decode tokens/s through vLLM with this backend (TP = N).
 `--impl reference` times the reference algorithm's CPU path (the oracle port; the Python
 reference tree itself is not present on the GPU machine) on a bounded sample per step.
 """
@@ -39,10 +43,11 @@ for _p in (ROOT, os.path.join(ROOT, "tt-xla_b200")):
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
-# DRAM traffic of the split-KV decode kernel, from the ncu capture of the small config-4 case
-# (profiles/decode_splitkv_c4.md): reads = 268.60 MB for 268.70 MB of algorithmic bytes, writes
-# = 6.25 MB for 8.52 MB of fp32 split partials (the rest is still in L2 when the combine reads
-# it).  Both parts grow in proportion to their own size, so a full launch is scaled from them.
+# DRAM traffic of the split-KV decode kernel as one `ncu --set full -k regex:paged_decode_splitkv`
+# capture of `bench.py --workload c4s` measured it: dram reads = 268.60 MB for 268.70 MB of
+# algorithmic bytes, dram writes = 6.25 MB for 8.52 MB of fp32 split partials (the rest is still
+# in L2 when it is merged).  Both parts grow in proportion to their own size, so a full launch
+# is scaled from them.  These are constants of that capture, not a live measurement.
 NCU_READ_PER_ALGORITHMIC_BYTE = 268.60 / 268.70
 NCU_WRITE_PER_PARTIAL_BYTE = 6.25 / 8.52
 FALLBACK_HBM_GBS = 6650.0
@@ -117,7 +122,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons = [], [], set()
+        sm, smax, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             parts = [x.strip() for x in ln.split(",")]
@@ -126,6 +131,7 @@ class ClockSampler:
             try:
                 sm.append(float(parts[1]))
                 smax.append(float(parts[2]))
+                power.append(float(parts[3]))
             except ValueError:
                 continue
             for name, val in zip(names, parts[4:8]):
@@ -133,7 +139,8 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "power_w_max": max(power) if power else None,
+                "reasons": sorted(reasons)}
 
 
 def decode_algorithmic_bytes(ctx_lens: torch.Tensor, nq: int, nkv: int, hd: int, bs: int,
@@ -145,19 +152,6 @@ def decode_algorithmic_bytes(ctx_lens: torch.Tensor, nq: int, nkv: int, hd: int,
     qo = 2 * users * nq * hd * 2
     meta = int(((ctx_lens + bs - 1) // bs).sum()) * 4 + 4 * users
     return kv + qo + meta
-
-
-def gen_cache(nb: int, nkv: int, bs: int, hd: int, seed: int, device,
-              dtype=torch.bfloat16) -> torch.Tensor:
-    """N(0,1) cache generated block-range by block-range so the fp32 temporaries stay small."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    out = torch.empty((nb, nkv, bs, hd), dtype=dtype, device=device)
-    step = max(1, (256 << 20) // (nkv * bs * hd * 4))
-    for b0 in range(0, nb, step):
-        b1 = min(nb, b0 + step)
-        out[b0:b1] = torch.randn((b1 - b0, nkv, bs, hd), generator=g, device=device,
-                                 dtype=torch.float32).to(dtype)
-    return out
 
 
 def dist_setup(n_gpus: int):
@@ -185,9 +179,35 @@ def max_over_ranks(x: float, world: int, device) -> float:
 
 
 # ------------------------------------------------------------------------------ workloads
+class StagedInputs:
+    """One pinned host buffer and one device buffer holding a step's inputs back to back (256-byte
+    aligned segments), so that a step's host-to-device transfer is a single copy."""
+
+    def __init__(self, tensors: dict, device):
+        self.offsets, total = {}, 0
+        for name, t in tensors.items():
+            self.offsets[name] = total
+            total += (t.numel() * t.element_size() + 255) // 256 * 256
+        self.host = torch.empty(total, dtype=torch.uint8).pin_memory()
+        self.dev = torch.empty(total, dtype=torch.uint8, device=device)
+        self.nbytes = total
+        self.h, self.d = {}, {}
+        for name, t in tensors.items():
+            o, n = self.offsets[name], t.numel() * t.element_size()
+            self.h[name] = self.host[o:o + n].view(t.dtype).view(t.shape)
+            self.d[name] = self.dev[o:o + n].view(t.dtype).view(t.shape)
+            self.h[name].copy_(t)
+
+    def upload(self):
+        self.dev.copy_(self.host, non_blocking=True)
+
+
 def make_decode_workload(wl: dict, rank: int, world: int, device):
-    """Per-rank tensors of the decode workload: this rank's KV heads of every block, its q heads,
-    and a replica of the int32 metadata."""
+    """Per-rank tensors of the decode workload: this rank's KV heads of every block (allocated
+    the way the plugin's runner allocates them, then filled with N(0,1)), its q heads, and a
+    replica of the int32 metadata."""
+    from b200attn import sharding
+
     nq, nkv, hd, bs, users = wl["nq"], wl["nkv"], wl["hd"], wl["bs"], wl["users"]
     if nkv % world != 0:
         raise SystemExit(f"{nkv} kv heads do not shard over {world} GPUs")
@@ -198,28 +218,73 @@ def make_decode_workload(wl: dict, rank: int, world: int, device):
     page_table = torch.randperm(nb, generator=g).reshape(users, nblk).to(torch.int32)
     nkv_l, nq_l = nkv // world, nq // world
     kv_dtype = torch.float8_e4m3fn if wl.get("kv_dtype") == "fp8_e4m3" else torch.bfloat16
-    k_cache = gen_cache(nb, nkv_l, bs, hd, 100 + rank, device, kv_dtype)
-    v_cache = gen_cache(nb, nkv_l, bs, hd, 200 + rank, device, kv_dtype)
+    k_cache, v_cache = sharding.allocate_kv_caches(["layer"], nb, nkv, bs, hd, dtype=kv_dtype,
+                                                   device=device, tp_size=world)["layer"]
+    fill_cache_randn(k_cache, 100 + rank)
+    fill_cache_randn(v_cache, 200 + rank)
     gq = torch.Generator().manual_seed(300 + rank)
-    host = dict(
-        q=torch.randn(users, nq_l * hd, generator=gq).to(torch.bfloat16).pin_memory(),
-        k=torch.randn(users, nkv_l * hd, generator=gq).to(torch.bfloat16).pin_memory(),
-        v=torch.randn(users, nkv_l * hd, generator=gq).to(torch.bfloat16).pin_memory(),
-        cache_position=(ctx - 1).to(torch.int32).pin_memory(),
-        page_table=page_table.pin_memory(),
-        out=torch.empty(users, nq_l * hd, dtype=torch.bfloat16).pin_memory(),
+    inputs = dict(
+        q=torch.randn(users, nq_l * hd, generator=gq).to(torch.bfloat16),
+        k=torch.randn(users, nkv_l * hd, generator=gq).to(torch.bfloat16),
+        v=torch.randn(users, nkv_l * hd, generator=gq).to(torch.bfloat16),
+        cache_position=(ctx - 1).to(torch.int32),
+        page_table=page_table,
     )
     return dict(nq=nq_l, nkv=nkv_l, hd=hd, bs=bs, users=users, ctx=ctx, nb=nb,
-                k_cache=k_cache, v_cache=v_cache, host=host, max_ctx=int(ctx.max()))
+                k_cache=k_cache, v_cache=v_cache, inputs=inputs, max_ctx=int(ctx.max()))
 
 
-def run_decode_bench(args, wl, rank, world, device):
+def fill_cache_randn(cache: torch.Tensor, seed: int) -> None:
+    """N(0,1) into an allocated cache, block range by block range so the fp32 temporaries stay
+    small."""
+    nb, nkv, bs, hd = cache.shape
+    g = torch.Generator(device=cache.device).manual_seed(seed)
+    step = max(1, (256 << 20) // (nkv * bs * hd * 4))
+    for b0 in range(0, nb, step):
+        b1 = min(nb, b0 + step)
+        cache[b0:b1] = torch.randn((b1 - b0, nkv, bs, hd), generator=g, device=cache.device,
+                                   dtype=torch.float32).to(cache.dtype)
+
+
+def oracle_check(w, out: torch.Tensor, users_to_check) -> dict:
+    """Compares the timed step's output rows of a few users with the CPU oracle (fp32 arithmetic
+    on the same cache contents, new token included), this rank's heads."""
+    from oracle import restate
+
+    nq, nkv, hd, bs = w["nq"], w["nkv"], w["hd"], w["bs"]
+    G = nq // nkv
+    scale = hd ** -0.5
+    pt = w["inputs"]["page_table"]
+    worst, total, count = 0.0, 0.0, 0
+    for u in users_to_check:
+        L = int(w["ctx"][u])
+        pages = pt[u, : (L + bs - 1) // bs].long()
+        kc = w["k_cache"][pages.to(w["k_cache"].device)].float().cpu()      # [pages, nkv, bs, hd]
+        vc = w["v_cache"][pages.to(w["v_cache"].device)].float().cpu()
+        local_pt = torch.arange(pages.numel(), dtype=torch.int32)[None]
+        q = w["inputs"]["q"][u].view(1, 1, nq, hd).float()
+        pos = torch.tensor([L - 1], dtype=torch.int32)
+        got = out[u].float().cpu().view(nq, hd)
+        for h in range(nkv):
+            want = restate.paged_sdpa_decode(q[:, :, h * G:(h + 1) * G], kc[:, h:h + 1],
+                                             vc[:, h:h + 1], local_pt, pos, scale)[0, 0]
+            d = (got[h * G:(h + 1) * G] - want).abs()
+            worst = max(worst, float(d.max()))
+            total += float(d.sum())
+            count += d.numel()
+    return {"users": list(users_to_check), "max_abs": worst, "mean_abs": total / max(count, 1)}
+
+
+def run_decode_bench(args, wl, rank, world, device, light: bool = False):
+    """Times the decode step of workload `wl`.  `light`: device-timed graph replays only (the
+    extra workloads reported beside the headline one)."""
     from b200attn import B200AttentionBackendImpl, B200Metadata, ops
 
     w = make_decode_workload(wl, rank, world, device)
     users, nq, nkv, hd, bs = w["users"], w["nq"], w["nkv"], w["hd"], w["bs"]
-    h = w["host"]
-    dev = {k: v.to(device) for k, v in h.items() if k != "out"}
+    staged = StagedInputs(w["inputs"], device)
+    staged.upload()
+    dev = staged.d
     out = torch.empty(users, nq * hd, dtype=torch.bfloat16, device=device)
     q3 = dev["q"].view(users, nq, hd)
     k3 = dev["k"].view(users, nkv, hd)
@@ -239,7 +304,7 @@ def run_decode_bench(args, wl, rank, world, device):
     # ---- timed region: K steps, device events, max over ranks; per-step decode-call events too
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(args.steps)]
-    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 and not light else None
     barrier(world)
     if sampler:
         sampler.start()
@@ -276,61 +341,112 @@ def run_decode_bench(args, wl, rank, world, device):
         graph.replay()
     g1.record()
     barrier(world)
-    clocks = sampler.stop() if sampler else None
     total_ms = max_over_ranks(g0.elapsed_time(g1), world, device)
     decode_ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
     decode_ms = max_over_ranks(decode_ms, world, device)
-    err = ops.read_error_word()
-    if err:
-        raise SystemExit(f"a kernel reported device error {err}")
-
-    # ---- e2e: through the backend's forward with pinned host inputs, output read back
-    impl = B200AttentionBackendImpl(nq, hd, scale, nkv, None, None,
-                                    "fp8_e4m3" if wl.get("kv_dtype") == "fp8_e4m3" else "auto")
-    kv = [w["k_cache"], w["v_cache"]]
-    d_q = torch.empty_like(dev["q"])
-    d_k = torch.empty_like(dev["k"])
-    d_v = torch.empty_like(dev["v"])
-    d_pos = torch.empty_like(dev["cache_position"])
-    d_pt = torch.empty_like(dev["page_table"])
-    md = B200Metadata(cache_position=d_pos, page_table=d_pt, num_users=users,
-                      batch_idx=torch.arange(users, dtype=torch.int32, device=device),
-                      max_seq_len=w["max_ctx"])
-    h2d = sum(h[k].numel() * h[k].element_size() for k in ("q", "k", "v", "cache_position",
-                                                             "page_table"))
-    d2h = h["out"].numel() * h["out"].element_size()
-
-    def e2e_step():
-        d_q.copy_(h["q"], non_blocking=True)
-        d_k.copy_(h["k"], non_blocking=True)
-        d_v.copy_(h["v"], non_blocking=True)
-        d_pos.copy_(h["cache_position"], non_blocking=True)
-        d_pt.copy_(h["page_table"], non_blocking=True)
-        impl.forward(None, d_q, d_k, d_v, kv, md, output=out)
-        h["out"].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for _ in range(max(3, args.warmup)):
-        e2e_step()
-    barrier(world)
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier(world)
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, device) / args.steps
-
     eb = w["k_cache"].element_size()
     full_bytes = decode_algorithmic_bytes(w["ctx"], wl["nq"], wl["nkv"], hd, bs, eb)
     rank_bytes = decode_algorithmic_bytes(w["ctx"], nq, nkv, hd, bs, eb)
     ms_per_step = total_ms / args.steps
-    return dict(w=w, full_bytes=full_bytes, rank_bytes=rank_bytes, ms_per_step=ms_per_step,
-                decode_ms=decode_ms, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h, clocks=clocks,
-                eager_ms_per_step=eager_ms / args.steps,
-                splits=splits, launches=(2 if splits > 1 else 1) * args.steps,
-                partial_bytes=ops.decode_workspace_bytes(users, nq, hd, splits))
+    res = dict(w=w, full_bytes=full_bytes, rank_bytes=rank_bytes, ms_per_step=ms_per_step,
+               decode_ms=decode_ms, eager_ms_per_step=eager_ms / args.steps, splits=splits,
+               launches=args.steps, out=out,
+               partial_bytes=ops.decode_workspace_bytes(users, nq, hd, splits))
+    if light:
+        err = ops.read_error_word()
+        if err:
+            raise SystemExit(f"a kernel reported device error {err}")
+        return res
+
+    # ---- sustained: rounds of K replays for about two seconds, each round timed on its own
+    rounds, spent = [], 0.0
+    while spent < args.sustain_s * 1e3 and len(rounds) < 2000:
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            graph.replay()
+        b.record()
+        b.synchronize()
+        rounds.append(a.elapsed_time(b) / args.steps)
+        spent += rounds[-1] * args.steps
+    barrier(world)
+    clocks = sampler.stop() if sampler else None
+    if rounds:
+        srt = sorted(rounds)
+        med = max_over_ranks(statistics.median(rounds), world, device)
+        res["sustained"] = {
+            "seconds": round(spent / 1e3, 2), "rounds": len(rounds),
+            "ms_per_step_median": round(med, 4),
+            "ms_per_step_p05": round(srt[len(srt) // 20], 4),
+            "ms_per_step_p95": round(srt[min(len(srt) - 1, len(srt) * 19 // 20)], 4),
+            "value_median": round(full_bytes / (med * 1e-3) / 1e9, 1), "unit": "GB/s"}
+    err = ops.read_error_word()
+    if err:
+        raise SystemExit(f"a kernel reported device error {err}")
+
+    # ---- parity of what was timed: a few users' rows against the CPU oracle
+    check = oracle_check(w, out, sorted({0, users - 1}))
+    check["max_abs"] = max_over_ranks(check["max_abs"], world, device)
+    check["mean_abs"] = max_over_ranks(check["mean_abs"], world, device)
+    check["tolerance"] = {"max_abs": 2e-2, "mean_abs": 2e-3}
+    check["ok"] = check["max_abs"] <= 2e-2 and check["mean_abs"] <= 2e-3
+    res["parity_check"] = check
+
+    # ---- e2e: through the backend's forward; the step's inputs go host -> device in ONE copy of
+    # a pinned staging buffer, the output comes back in one copy, the host waits for it
+    impl = B200AttentionBackendImpl(nq, hd, scale, nkv, None, None,
+                                    "fp8_e4m3" if wl.get("kv_dtype") == "fp8_e4m3" else "auto")
+    kv = [w["k_cache"], w["v_cache"]]
+    md = B200Metadata(cache_position=dev["cache_position"], page_table=dev["page_table"],
+                      num_users=users,
+                      batch_idx=torch.arange(users, dtype=torch.int32, device=device),
+                      max_seq_len=w["max_ctx"])
+    h_out = torch.empty(users, nq * hd, dtype=torch.bfloat16).pin_memory()
+    h2d, d2h = staged.nbytes, h_out.numel() * h_out.element_size()
+
+    def e2e_body():
+        staged.upload()
+        impl.forward(None, dev["q"], dev["k"], dev["v"], kv, md, output=out)
+        h_out.copy_(out, non_blocking=True)
+
+    def timed_e2e(run_one):
+        for _ in range(max(3, args.warmup)):
+            run_one()
+        barrier(world)
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            run_one()
+        e1.record()
+        barrier(world)
+        return max_over_ranks(e0.elapsed_time(e1), world, device) / args.steps
+
+    def eager_one():
+        e2e_body()
+        torch.cuda.current_stream().synchronize()
+
+    e2e_eager_ms = timed_e2e(eager_one)
+    # The same step (copy in, forward, copy out) captured once and replayed, the way a serving
+    # engine runs a decode step; the host still waits for every step's output.
+    e2e_graph = torch.cuda.CUDAGraph()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        e2e_body()
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(e2e_graph, stream=side):
+        e2e_body()
+
+    def graph_one():
+        e2e_graph.replay()
+        torch.cuda.current_stream().synchronize()
+
+    e2e_ms = timed_e2e(graph_one)
+    e2e_check = (h_out.float() - out.float().cpu()).abs().max().item()
+    res.update(e2e_ms=e2e_ms, e2e_eager_ms=e2e_eager_ms, h2d=h2d, d2h=d2h, clocks=clocks,
+               e2e_readback_matches=e2e_check == 0.0)
+    return res
 
 
 def run_prefill_bench(args, rank, world, device, peaks):
@@ -440,23 +556,18 @@ LLAMA31_8B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden
                   tie_word_embeddings=False, hidden_act="silu", bos_token_id=1, eos_token_id=2)
 
 
-def run_rowlinear_bench(args):
+def measure_rowlinear(args, rank, world, device, steps=None):
     """Row-parallel linear + all-reduce of the end-to-end model's decode step (config 5: 64 token
     rows, hidden 4096, o_proj K = 4096 / TP and down_proj K = 14336 / TP): the fused launch of
     this repository against torch's GEMM followed by an NCCL all-reduce, both walking a set of 32
     different weight matrices (one per layer, larger than L2 together) as the model does.  Device
-    time by CUDA events, max over ranks."""
-    rank, world, local = dist_setup(args.gpus)
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    sys.path.insert(0, os.path.join(ROOT, "tt-xla_b200"))
+    time by CUDA events, max over ranks.  Also checks the fused result: error against an fp32
+    all-reduce of fp32 partial products, and that every rank holds the same bits."""
     from b200attn import ops, tp_linear
 
+    steps = steps or args.steps
     comm = tp_linear.RowLinearComm(dist.group.WORLD, max_n=4096, max_tokens=128) if world > 1 else None
     tokens, hidden, layers = 64, 4096, 32
-    peaks = load_peaks()
     results = {}
     for name, k_full in (("o_proj", 4096), ("down_proj", 14336)):
         kl = k_full // world
@@ -489,11 +600,11 @@ def run_rowlinear_bench(args):
             barrier(world)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 graph.replay()
             e1.record()
             torch.cuda.synchronize()
-            return max_over_ranks(e0.elapsed_time(e1) * 1e3 / (args.steps * layers), world, device)
+            return max_over_ranks(e0.elapsed_time(e1) * 1e3 / (steps * layers), world, device)
 
         us_stock = timed(stock)
         us_fused = timed(fused)
@@ -501,14 +612,42 @@ def run_rowlinear_bench(args):
         if world > 2:       # both exchange schemes, for the record (the default picks two shots)
             by_mode = {"one_shot_us": round(timed(lambda: fused(1)), 2),
                        "two_shot_us": round(timed(lambda: fused(2)), 2)}
+        # correctness of what was timed: last layer's result against fp32 arithmetic
+        tp_linear.rowlinear_allreduce(x, ws[-1], comm, out=out)
+        ref = x.float() @ ws[-1].float().t()
+        if world > 1:
+            dist.all_reduce(ref)
+        err = max_over_ranks(float((out.float() - ref).abs().max()), world, device)
+        digest = out.view(torch.int16).to(torch.int64).sum().reshape(1)
+        same = True
+        if world > 1:
+            digests = [torch.empty_like(digest) for _ in range(world)]
+            dist.all_gather(digests, digest)
+            same = all(int(d) == int(digests[0]) for d in digests)
         wbytes = hidden * kl * 2
         results[name] = {"k_local": kl, "fused_us": round(us_fused, 2), "stock_us": round(us_stock, 2),
                          "weight_gbs_fused": round(wbytes / us_fused / 1e3, 1),
-                         "weight_gbs_stock": round(wbytes / us_stock / 1e3, 1), **by_mode}
+                         "weight_gbs_stock": round(wbytes / us_stock / 1e3, 1),
+                         "max_abs_err_vs_fp32": round(err, 5), "all_ranks_identical": same,
+                         **by_mode}
     word = ops.read_error_word()
     if comm is not None:
         dist.barrier()
         comm.close()
+    results["error_word"] = word
+    results["stock"] = "torch.matmul + NCCL all-reduce"
+    results["form"] = "64 token rows, N 4096, 32 distinct weights per pass, CUDA-graph replay"
+    return results
+
+
+def run_rowlinear_bench(args):
+    rank, world, local = dist_setup(args.gpus)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    peaks = load_peaks()
+    results = measure_rowlinear(args, rank, world, device)
     if rank == 0:
         o = results["o_proj"]
         print(json.dumps({
@@ -520,7 +659,7 @@ def run_rowlinear_bench(args):
                        "parallelism": f"tp{world}", "step": "32 layers back to back, replayed as one CUDA graph",
                        "l2": "32 distinct weight matrices per pass (larger than L2 together)",
                        "stock": "torch.matmul + NCCL all-reduce"},
-            "layers": results, "error_word": word,
+            "layers": results, "error_word": results["error_word"],
             "roofline": {"bound": "hbm", "achieved": o["weight_gbs_fused"], "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(o["weight_gbs_fused"] / peaks["hbm_gbs"], 4),
                          "traffic": None, "peak_source": peaks["source"],
@@ -529,6 +668,39 @@ def run_rowlinear_bench(args):
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_e2e_model_subprocess(args, rank: int, world: int, timeout_s: int = 600):
+    """Config 5 (end-to-end Llama-3.1-8B decode through vLLM, `--workload c5`) as a child process
+    of every rank, so that the engine gets a fresh CUDA context and its own process group.
+    Returns rank 0's result line as a dict (None on the other ranks)."""
+    env = dict(os.environ)
+    if world > 1:
+        # a rendezvous of its own: the parent's store keeps serving the parent's group
+        env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 23)
+        for k in ("TORCHELASTIC_USE_AGENT_STORE", "TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT",
+                  "TORCHELASTIC_MAX_RESTARTS", "TORCHELASTIC_ERROR_FILE"):
+            env.pop(k, None)
+    cmd = [sys.executable, os.path.abspath(__file__), "--workload", "c5", "--gpus", str(world),
+           "--steps", "1"]
+    if args.fused_linear:
+        cmd.append("--fused-linear")
+    try:
+        proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"config 5 did not finish within {timeout_s} s"} if rank == 0 else None
+    if rank != 0:
+        return None
+    for ln in reversed(proc.stdout.splitlines()):
+        if ln.startswith("{") and '"e2e_decode_tokens_per_s"' in ln:
+            d = json.loads(ln)
+            return {"metric": d["metric"], "value": d["value"], "unit": d["unit"],
+                    "ms_per_step": d["ms_per_step"], "ttft_s": d["ttft_s"],
+                    "generate_s": d["generate_s"], "tokens": d["tokens"],
+                    "error_word": d["error_word"], "config": d["config"],
+                    "roofline": d["roofline"]}
+    tail = (proc.stderr or proc.stdout)[-400:].replace("\n", " | ")
+    return {"unavailable": f"config 5 child exited {proc.returncode}: {tail}"}
 
 
 def run_e2e_llama(args):
@@ -642,45 +814,67 @@ def cpu_decode_sample(wl: dict, n_users: int, seed: int = 0):
     return dict(ctx=ctx, pt=pt, kc=kc, vc=vc, q=q, k=k, v=v, pos=(ctx - 1).to(torch.int32))
 
 
-def cpu_decode_step(s, hd: int):
-    """The reference's decode step on CPU: two cache writes and the paged decode attention.
-    The functional full-cache clone of the reference's cache write is part of what it does."""
+def cpu_cache_write(s):
+    """The reference's decode-step cache write on CPU: `paged_update_cache` for K and for V.  The
+    op is functional, so each call clones the whole pool (custom_ops.py:982); that clone is
+    part of what the reference does and dominates this timing."""
     from oracle import restate
 
     kc = restate.paged_update_cache(s["kc"], s["k"], s["pos"], s["pt"])
     vc = restate.paged_update_cache(s["vc"], s["v"], s["pos"], s["pt"])
+    return kc, vc
+
+
+def cpu_decode_attention(s, kc, vc, hd: int):
+    """The reference's paged decode attention on CPU over an already written cache."""
+    from oracle import restate
+
     return restate.paged_sdpa_decode(s["q"], kc, vc, s["pt"], s["pos"], hd ** -0.5)
 
 
+def time_cpu(fn, budget_s: float, max_reps: int = 50):
+    reps, spent = 0, 0.0
+    while reps < 1 or (spent < budget_s and reps < max_reps):
+        t0 = time.perf_counter()
+        fn()
+        spent += time.perf_counter() - t0
+        reps += 1
+    return spent / reps, reps, spent
+
+
 def run_cpu_baseline(wl: dict, budget_s: float = 12.0, max_users: int = 16):
-    """Times the oracle port on a bounded sample: up to `max_users` users of the batch, repeated
-    until about `budget_s` seconds of CPU work have been spent."""
+    """Times the oracle port on a bounded sample: up to `max_users` users of the batch.  The
+    decode attention and the cache write are timed apart: `value` is the attention alone (the
+    metric is attention bytes per second); the write, whose cost on CPU is the functional clone
+    of the whole pool, is reported beside it."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     s = cpu_decode_sample(wl, 1)
+    kc, vc = cpu_cache_write(s)
     t0 = time.perf_counter()
-    cpu_decode_step(s, wl["hd"])
+    cpu_decode_attention(s, kc, vc, wl["hd"])
     t1 = time.perf_counter() - t0
-    users = int(max(1, min(max_users, wl["users"], budget_s / max(t1, 1e-3))))
+    users = int(max(1, min(max_users, wl["users"], 0.75 * budget_s / max(t1, 1e-3))))
     if users > 1:
         s = cpu_decode_sample(wl, users)
-    reps, spent = 0, 0.0
-    while reps < 1 or (spent < budget_s and reps < 50):
-        t0 = time.perf_counter()
-        cpu_decode_step(s, wl["hd"])
-        spent += time.perf_counter() - t0
-        reps += 1
-    per_step = spent / reps
+        kc, vc = cpu_cache_write(s)
+    attn_s, reps, spent = time_cpu(lambda: cpu_decode_attention(s, kc, vc, wl["hd"]),
+                                   0.75 * budget_s)
+    write_s, wreps, wspent = time_cpu(lambda: cpu_cache_write(s), 0.25 * budget_s, 10)
     nbytes = decode_algorithmic_bytes(s["ctx"], wl["nq"], wl["nkv"], wl["hd"], wl["bs"])
-    return {"value": round(nbytes / per_step / 1e9, 4), "unit": "GB/s", "cores": cores,
+    return {"value": round(nbytes / attn_s / 1e9, 4), "unit": "GB/s", "cores": cores,
             "kind": "port",
-            "sample": f"{users} of {wl['users']} users of the batch, all heads, native bf16, "
-                      f"cache write + decode attention, {reps} repetitions, {spent:.1f} s in all"}
+            "attention_ms": round(attn_s * 1e3, 2), "cache_write_ms": round(write_s * 1e3, 2),
+            "value_with_cache_write": round(nbytes / (attn_s + write_s) / 1e9, 4),
+            "sample": f"{users} of {wl['users']} users of the batch, all heads, native bf16; decode "
+                      f"attention alone: {reps} repetitions, {spent:.1f} s; cache write (two "
+                      f"functional clones of the sample's pool): {wreps} repetitions, {wspent:.1f} s"}
 
 
 def run_reference_arm(args, wl):
     """The reference algorithm's CPU path (oracle port) on this machine's cores: every step is
-    one user of the batch through cache write + decode attention."""
+    the paged decode attention of one user of the batch (the cache write is timed apart and
+    reported beside it: on CPU it is a functional clone of the pool)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -688,25 +882,36 @@ def run_reference_arm(args, wl):
     torch.set_num_threads(cores)
     s = cpu_decode_sample(wl, 1)
     nbytes = decode_algorithmic_bytes(s["ctx"], wl["nq"], wl["nkv"], wl["hd"], wl["bs"])
+    kc, vc = cpu_cache_write(s)
     for _ in range(args.warmup):
-        cpu_decode_step(s, wl["hd"])
+        cpu_decode_attention(s, kc, vc, wl["hd"])
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_decode_step(s, wl["hd"])
+        cpu_decode_attention(s, kc, vc, wl["hd"])
     dt = (time.perf_counter() - t0) / args.steps
+    write_s, _, _ = time_cpu(lambda: cpu_cache_write(s), 2.0, 5)
     val = round(nbytes / dt / 1e9, 4)
-    sample = f"1 of {wl['users']} users per step, all heads, native bf16, {dt:.2f} s per step"
+    sample = (f"1 of {wl['users']} users per step, all heads, native bf16, decode attention "
+              f"{dt:.2f} s per step; cache write apart: {write_s:.2f} s")
     print(json.dumps({
         "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl["desc"], "parallelism": "cpu host cores"},
+        "config": workload_config(wl, args.gpus, parallelism="cpu host cores"),
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": sample},
+                         "cache_write_ms": round(write_s * 1e3, 2), "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def workload_config(wl: dict, world: int, parallelism: str) -> dict:
+    """The `config` object both arms print: the workload and its geometry."""
+    return {"workload": wl["desc"], "parallelism": parallelism, "q_heads": wl["nq"],
+            "kv_heads": wl["nkv"], "head_dim": wl["hd"], "block_size": wl["bs"],
+            "batch": wl["users"], "kv_cache_dtype": wl.get("kv_dtype", "bf16"),
+            "context": [wl["ctx_lo"], wl["ctx_hi"]]}
 
 
 # ------------------------------------------------------------------------------ main
@@ -720,9 +925,15 @@ def main():
     ap.add_argument("--attn", default="b200", choices=["b200", "stock"],
                     help="c5 only: this repository's backend, or vLLM's stock one for comparison")
     ap.add_argument("--fused-linear", action="store_true",
-                    help="c5 only: o_proj / down_proj through the fused GEMM + all-reduce launch")
+                    help="c5: o_proj / down_proj through the fused GEMM + all-reduce launch")
+    ap.add_argument("--sustain-s", type=float, default=2.0,
+                    help="seconds of back-to-back graph replays reported beside the K-step number")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra workloads (configs 1 and 3, the row-parallel linear)")
+    ap.add_argument("--no-e2e-model", action="store_true",
+                    help="skip config 5 (end-to-end Llama-3.1-8B through vLLM, a child process)")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="prefill: run only the config-2 prefill part (profiling aid)")
     args = ap.parse_args()
@@ -768,15 +979,37 @@ def main():
         return
 
     r = run_decode_bench(args, wl, rank, world, device)
+    del r["w"], r["out"]
+    torch.cuda.empty_cache()
     prefill = None if args.no_prefill else run_prefill_bench(args, rank, world, device, peaks)
-    chunks = run_chunk_bench(args, rank, world, device, peaks) if args.workload == "c3" else None
-    w = r["w"]
-    del r["w"]
+    chunks = None
+    extras = {}
+    if not args.no_extras and args.workload == "c4":
+        chunks = run_chunk_bench(args, rank, world, device, peaks)
+        for name in ("c1", "c3"):
+            x = run_decode_bench(args, WORKLOADS[name], rank, world, device, light=True)
+            gbs = x["full_bytes"] / (x["ms_per_step"] * 1e-3) / 1e9
+            extras[name] = {"workload": WORKLOADS[name]["desc"],
+                            "ms_per_step": round(x["ms_per_step"], 4),
+                            "decode_attn_hbm_gbs": round(gbs, 1), "num_splits": x["splits"],
+                            "frac_of_hbm_peak": round(gbs / (peaks["hbm_gbs"] * world), 4),
+                            "timing": "CUDA-graph replays of the decode step, device events"}
+            del x
+            torch.cuda.empty_cache()
+        if world > 1:
+            extras["rowlinear"] = measure_rowlinear(args, rank, world, device)
+    elif args.workload == "c3":
+        chunks = run_chunk_bench(args, rank, world, device, peaks)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and "kv_dtype" not in wl:
-        w = None
-        torch.cuda.empty_cache()
         cpu = run_cpu_baseline(wl)
+    e2e_model = None
+    if not args.no_e2e_model and args.workload == "c4":
+        # the engine gets the GPUs to itself: this process keeps only its CUDA context
+        torch.cuda.empty_cache()
+        barrier(world)
+        e2e_model = run_e2e_model_subprocess(args, rank, world)
+        barrier(world)
 
     if rank == 0:
         value = r["full_bytes"] / (r["ms_per_step"] * 1e-3) / 1e9
@@ -784,33 +1017,41 @@ def main():
         achieved = r["rank_bytes"] / (r["decode_ms"] * 1e-3) / 1e9
         traffic = int(r["rank_bytes"] * NCU_READ_PER_ALGORITHMIC_BYTE
                       + r["partial_bytes"] * NCU_WRITE_PER_PARTIAL_BYTE)
+        config = workload_config(wl, world, parallelism=f"kv_head_shard{world}")
+        config.update({
+            "num_splits": r["splits"],
+            "step": "one launch: the split-KV decode kernel writes the new K/V rows, streams the "
+                    "cache and merges its splits; replayed as one CUDA graph",
+            "eager_ms_per_step": round(r["eager_ms_per_step"], 4),
+            "l2": "inputs larger than L2 (per-rank KV stream "
+                  f"{r['rank_bytes'] / 1e6:.0f} MB vs 126 MB)"})
         line = {
             "metric": "decode_attn_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl["desc"], "parallelism": f"kv_head_shard{world}",
-                       "q_heads": wl["nq"], "kv_heads": wl["nkv"], "head_dim": wl["hd"],
-                       "block_size": wl["bs"], "batch": wl["users"],
-                       "kv_cache_dtype": wl.get("kv_dtype", "bf16"),
-                       "context": [wl["ctx_lo"], wl["ctx_hi"]], "num_splits": r["splits"],
-                       "step": "split-KV decode launch that also writes the new K/V rows, + combine; replayed as "
-                               "one CUDA graph",
-                       "eager_ms_per_step": round(r["eager_ms_per_step"], 4),
-                       "l2": "inputs larger than L2 (per-rank KV stream "
-                             f"{r['rank_bytes'] / 1e6:.0f} MB vs 126 MB)"},
+            "config": config,
             "clocks": r["clocks"],
+            "sustained": r.get("sustained"),
+            "parity_check": r["parity_check"],
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": r["h2d"] * world,
-                    "d2h_bytes_per_step": r["d2h"] * world, "ms_per_step": round(r["e2e_ms"], 4)},
+                    "d2h_bytes_per_step": r["d2h"] * world, "ms_per_step": round(r["e2e_ms"], 4),
+                    "form": "B200AttentionBackendImpl.forward between one pinned host-to-device "
+                            "copy of the step's inputs and the device-to-host copy of its output, "
+                            "captured once and replayed as a CUDA graph; the host waits for every "
+                            "step's output",
+                    "eager_ms_per_step": round(r["e2e_eager_ms"], 4),
+                    "readback_matches_device": r["e2e_readback_matches"]},
             "gpu_launches": r["launches"],
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                          "traffic": None if "kv_dtype" in wl else traffic,
                          "traffic_source": "not captured for the fp8 kernel" if "kv_dtype" in wl
-                         else "ncu capture of the small case, scaled",
+                         else "constant ratios from one ncu capture of the c4s workload, scaled "
+                              "to this launch (not measured in this run)",
                          "peak_source": peaks["source"],
                          "kernel": ("paged_decode_fp8_kernel" if "kv_dtype" in wl
-                                    else "paged_decode_splitkv_kernel") + " + decode_combine_kernel",
+                                    else "paged_decode_splitkv_kernel"),
                          "ms_per_launch": round(r["decode_ms"], 4),
                          "algorithmic_bytes_per_launch": r["rank_bytes"]},
             "cpu_baseline": cpu,
@@ -819,10 +1060,16 @@ def main():
             line["prefill"] = prefill
         if chunks:
             line["prefill_chunks"] = chunks
+        if extras:
+            line["extra_workloads"] = extras
+        if e2e_model is not None:
+            line["e2e_model"] = e2e_model
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not r["parity_check"]["ok"]:
+        raise SystemExit(f"parity check failed: {r['parity_check']}")
 
 
 if __name__ == "__main__":

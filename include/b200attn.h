@@ -53,7 +53,9 @@ enum b200attn_status {
 /* Device-side diagnostics word values (see b200attn_read_error_word). */
 enum b200attn_device_error {
   B200ATTN_DEV_OK = 0,
-  B200ATTN_DEV_WAIT_TIMEOUT = 1,   /* a bounded mbarrier wait ran out */
+  B200ATTN_DEV_WAIT_TIMEOUT = 1,   /* a bounded wait ran out; CTAs that start within the next second
+                                      return without writing their output, later launches run
+                                      normally; the word stays set until it is read */
   B200ATTN_DEV_BAD_INDEX = 2       /* a page id or slot was outside the cache */
 };
 
@@ -159,16 +161,24 @@ int b200attn_rope_kv_scatter_slots(void* q, int64_t q_stride, void* k, int64_t k
                                    void* stream);
 
 /* ------------------------------------------------------------------------------------------
- * Paged GQA decode attention (one query token per user), split-KV + combine.
+ * Paged GQA decode attention (one query token per user), split-KV with the merge of the
+ * splits inside the same launch.
  * Replaces: torch.ops.tt.paged_scaled_dot_product_attention_decode with is_causal=True and
  *           cur_pos_tensor (custom_ops.py:1198-1331; call site attention.py:634-668).
  * out[u,h,:] = softmax_{j <= cur_pos[u]}(q[u,h,:] . K_u[j, h/G, :] * scale) . V_u[j, h/G, :]
  * where K_u/V_u are read through page_table[u, j / block_size].  Users with cur_pos < 0
  * (padding rows) get zeros.  q and out are [num_users, num_q_heads, head_size] with the
  * given row strides (elements).
- * num_splits: 0 = choose (b200attn_decode_auto_splits with max_context_len); the workspace
- * must hold b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size, num_splits)
- * bytes (it may be NULL when the split count in effect is 1).
+ * num_splits: 0 = choose (b200attn_decode_auto_splits with max_context_len), at most 256; the
+ * workspace must hold b200attn_decode_workspace_bytes(num_users, num_q_heads, head_size,
+ * num_splits) bytes (it may be NULL when the split count in effect is 1).
+ * Workspace contract: its first B200ATTN_DECODE_TICKET_BYTES bytes are arrival counters (one
+ * per user and KV head; the split that arrives last merges the partials).  They must be ZERO
+ * when the workspace is first used and every call leaves them zero, so zero the workspace once
+ * after allocating it and again after a call that left a non-zero diagnostics word.  The rest
+ * needs no initialisation.  Calls that share a workspace must not overlap on the GPU.  Batches
+ * with more than B200ATTN_DECODE_TICKET_BYTES / 4 (user, KV head) pairs use a second, small
+ * launch for the merge instead of the counters.
  * ------------------------------------------------------------------------------------------ */
 int b200attn_paged_decode(void* out, int64_t out_row_stride,
                           const void* q, int64_t q_row_stride,
@@ -234,10 +244,13 @@ int b200attn_kv_scatter_slots_ex(void* k_cache, void* v_cache,
  *     stream capture.
  *   - The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - All calls on a device share the one array and it keeps the previous call's contents.
- *     Nothing in it has to start at zero (every slot that is read was written by the same
- *     call), but two calls that overlap on the GPU -- different streams, or one stream from
- *     two threads without ordering -- race on it.  Serialise them.
+ *     The arrival counters at its start have to be zero when a call begins; the entry point
+ *     clears the ones the call will use (a cudaMemsetAsync on the same stream, which allocates
+ *     nothing) before it launches, the rest of the array needs no clearing (every slot that is
+ *     read was written by the same call).  Two calls that overlap on the GPU -- different
+ *     streams, or one stream from two threads without ordering -- race on it.  Serialise them.
  * ------------------------------------------------------------------------------------------ */
+#define B200ATTN_DECODE_TICKET_BYTES 65536u
 #define B200ATTN_STATIC_WORKSPACE_BYTES (16u << 20)
 int b200attn_paged_decode_static(void* out, int64_t out_row_stride,
                                  const void* q, int64_t q_row_stride,
@@ -300,7 +313,8 @@ int b200attn_paged_decode_step(void* out, int64_t out_row_stride,
 int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
                                 int max_context_len);
 
-/* Bytes of scratch b200attn_paged_decode needs for num_splits splits (0 when num_splits <= 1). */
+/* Bytes of scratch b200attn_paged_decode needs for num_splits splits (0 when num_splits <= 1):
+ * the ticket region, the fp32 partial outputs and their (max, sum) pairs. */
 size_t b200attn_decode_workspace_bytes(int num_users, int num_q_heads, int head_size,
                                        int num_splits);
 
@@ -379,9 +393,10 @@ int b200attn_prefill_ex(void* out, int64_t out_row_stride,
  *
  * All ranks must issue the same sequence of calls with the same shapes on one stream each.  The
  * call is asynchronous and allocation-free.  A peer that does not arrive within peer_timeout_ns
- * (0 = 10 s) makes the kernel give up: the diagnostics word becomes 1, the output of that call is
- * unspecified, later calls return at once, and the communicator must be rebuilt (collectively)
- * after the word has been read.  n_total, k_local and the strides must be multiples of 8;
+ * (0 = 1 s) makes the kernel give up: the diagnostics word becomes 1, the communicator buffer of
+ * this rank is marked out of step, the output of that call is unspecified, later calls through
+ * the same communicator only run their local GEMM, and the communicator must be rebuilt
+ * (collectively; a fresh buffer starts clean).  n_total, k_local and the strides must be multiples of 8;
  * n_total / 32 (or / 64) must not exceed the SM count (every CTA has to be resident). */
 size_t b200attn_comm_bytes(int world, int max_tokens, int max_n);
 /* The launch geometry b200attn_rowlinear_allreduce picks on the current device: token rows of
@@ -405,6 +420,13 @@ int b200attn_rowlinear_allreduce(void* out, int64_t out_row_stride,
 /* Copies the device diagnostics word of the current device to *out_host (synchronises the
  * stream) and clears it.  0 = no kernel reported a problem since the last read. */
 int b200attn_read_error_word(int32_t* out_host, void* stream);
+
+/* Queues an asynchronous copy of the diagnostics word to *out_pinned_host (page-locked host
+ * memory the caller owns) on `stream`; nothing is cleared and nothing is waited for.  A serving
+ * loop calls it once per step and looks at the value a later step finds there, so a kernel that
+ * gave up on a wait is noticed within a step or two without a synchronisation of its own.
+ * No counterpart in the reference (its runtime reports device errors through PJRT). */
+int b200attn_peek_error_word_async(int32_t* out_pinned_host, void* stream);
 
 #ifdef __cplusplus
 }

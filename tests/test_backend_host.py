@@ -118,3 +118,63 @@ def test_builder_returns_stub_without_varlen_fields():
         causal = True
     md = B200AttentionMetadataBuilder().build(0, Common())
     assert isinstance(md, B200Metadata) and md.cache_position is None and md.is_causal
+
+
+def test_padding_rows_of_the_decode_position_buffer_read_minus_one():
+    """A CUDA graph captured at a padded batch reads past this step's decode rows: a shrinking
+    batch must leave -1 there, not an earlier step's positions."""
+    buf = torch.full((8,), -1, dtype=torch.int32)
+    bt = torch.zeros(8, 4, dtype=torch.int32)
+
+    def step(seq_lens):
+        n = len(seq_lens)
+        qsl = torch.arange(n + 1, dtype=torch.int32)
+        return backend.build_varlen_metadata(qsl, qsl.clone(), torch.tensor(seq_lens, dtype=torch.int32),
+                                             bt[:n], torch.zeros(n, dtype=torch.int64),
+                                             decode_cur_pos_buffer=buf)
+
+    md = step([10, 20, 30, 40, 50])
+    assert md.decode_cur_pos.tolist() == [9, 19, 29, 39, 49] and buf.tolist()[5:] == [-1, -1, -1]
+    md = step([11, 21])
+    assert md.decode_cur_pos.tolist() == [10, 20]
+    assert buf.tolist() == [10, 20, -1, -1, -1, -1, -1, -1]
+
+
+def test_allocate_kv_caches_per_rank_and_shared_layers():
+    from b200attn import sharding
+
+    caches = sharding.allocate_kv_caches(3, 16, 8, 64, 128, tp_size=4,
+                                         shared_kv_layers={"layers.2.attn": "layers.0.attn"})
+    assert list(caches) == ["layers.0.attn", "layers.1.attn", "layers.2.attn"]
+    k, v = caches["layers.1.attn"]
+    assert k.shape == v.shape == (16, 2, 64, 128) and k.dtype == torch.bfloat16
+    assert k.data_ptr() != v.data_ptr() and float(k.abs().sum()) == 0
+    assert caches["layers.2.attn"] is caches["layers.0.attn"]
+    with pytest.raises(AssertionError, match="must be divisible by tp_size 3"):
+        sharding.allocate_kv_caches(1, 16, 8, 64, 128, tp_size=3)
+    with pytest.raises(ValueError, match="unknown layer"):
+        sharding.allocate_kv_caches(["a"], 4, 8, 64, 128, shared_kv_layers={"b": "c"})
+    f8 = sharding.allocate_kv_caches(["a"], 4, 8, 32, 128, dtype=torch.float8_e4m3fn)
+    assert f8["a"][0].dtype == torch.float8_e4m3fn
+
+    class Layer:
+        kv_cache = None
+    layers = {"layers.0.attn": Layer(), "other": Layer()}
+    sharding.bind_kv_caches(layers, caches)
+    assert layers["layers.0.attn"].kv_cache is caches["layers.0.attn"]
+    assert layers["other"].kv_cache is None
+
+
+def test_layer_wrapper_input_rules():
+    """attention.py:798-825: rank >= 2, hidden-width or (heads, head_size) trailing dims."""
+    assert backend.flatten_heads(torch.zeros(2, 3, 8, 64), "query", 8, 64).shape == (6, 512)
+    assert backend.flatten_heads(torch.zeros(2, 3, 512), "query", 8, 64).shape == (6, 512)
+    assert backend.flatten_heads(None, "key", 8, 64) is None
+    with pytest.raises(ValueError, match="rank >= 2"):
+        backend.flatten_heads(torch.zeros(512), "query", 8, 64)
+    with pytest.raises(ValueError, match="must satisfy one of"):
+        backend.flatten_heads(torch.zeros(4, 100), "value", 2, 64)
+    layer = backend.B200Attention(8, 64, 0.125, num_kv_heads=2, sliding_window=128)
+    assert layer.impl.num_kv_heads == 2 and layer.impl.sliding_window == 128
+    with pytest.raises(TypeError, match="unexpected arguments"):
+        backend.B200Attention(8, 64, 0.125, bogus=1)

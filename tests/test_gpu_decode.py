@@ -98,10 +98,10 @@ def test_decode_is_deterministic(clean_error_word):
 
 
 def test_long_context_property(clean_error_word):
-    """Config-4 shape (nq 64, nkv 8, hd 128, bs 64) at 32768 context, too large for the oracle
-    in seconds: V rows all equal to one vector => the output equals that vector whatever
-    the scores (softmax weights sum to 1); then a two-segment check against the oracle on one
-    user with a short second batch."""
+    """Config-4 shape (nq 64, nkv 8, hd 128, bs 64) at 32768 context: V rows all equal to one
+    vector => the output equals that vector whatever the scores (softmax weights sum to 1).  A
+    property of the normalisation only; the comparison with the oracle at this size is in
+    test_gpu_baseline_sizes.py."""
     from b200attn import ops
 
     users, nq, nkv, hd, bs, ctx = 2, 64, 8, 128, 64, 32768
@@ -117,3 +117,40 @@ def test_long_context_property(clean_error_word):
     out = ops.paged_decode(q, kc, vc, pt, pos, scale=hd ** -0.5)
     want = vec[:, 0].repeat_interleave(nq // nkv, 0).float()       # [nq, hd]
     assert (out.float() - want[None]).abs().max().item() <= 2e-2
+
+
+def test_split_merge_inside_the_launch_leaves_the_workspace_reusable(clean_error_word):
+    """The last split to arrive merges the partials and resets its arrival counter: the same
+    workspace serves calls of different shapes back to back, results bit-identical to a fresh
+    zeroed workspace."""
+    from b200attn import ops
+
+    ws = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
+    for seed, (users, nq, nkv, hd, bs, splits) in enumerate(
+            [(5, 32, 8, 128, 64, 4), (9, 8, 2, 64, 32, 3), (5, 32, 8, 128, 64, 7), (2, 16, 1, 128, 32, 16)]):
+        case = make_decode_case(nq=nq, nkv=nkv, hd=hd, bs=bs, users=users, ctx_lo=1, ctx_hi=900,
+                                seed=seed)
+        args = (case.q.reshape(users, nq, hd).cuda(), case.k_cache.cuda(), case.v_cache.cuda(),
+                case.page_table.cuda(), case.cache_position.cuda())
+        shared = ops.paged_decode(*args, scale=case.scale, num_splits=splits, workspace=ws)
+        fresh = ops.paged_decode(*args, scale=case.scale, num_splits=splits,
+                                 workspace=torch.zeros_like(ws))
+        assert torch.equal(shared, fresh)
+        assert_attention_close(shared.cpu(), oracle_decode(case), f"case {seed}")
+        assert int(ws[:65536].view(torch.int32).abs().sum()) == 0     # counters back at zero
+
+
+def test_batches_beyond_the_ticket_region_use_the_separate_merge(clean_error_word):
+    """More (user, KV head) pairs than arrival counters: the partials are merged by the second
+    launch, same results."""
+    users, nq, nkv, hd, bs = 4100, 4, 4, 64, 32
+    case = make_decode_case(nq=nq, nkv=nkv, hd=hd, bs=bs, users=users, ctx_lo=1, ctx_hi=96, seed=21)
+    assert users * nkv * 4 > 65536
+    out = run_decode(case, 2)
+    pick = torch.arange(0, users, 37)
+    sub = make_decode_case(nq=nq, nkv=nkv, hd=hd, bs=bs, users=users, ctx_lo=1, ctx_hi=96, seed=21)
+    want = restate.paged_sdpa_decode(
+        case.q.reshape(1, users, nq, hd)[:, pick].float(), sub.k_cache.float(), sub.v_cache.float(),
+        case.page_table[pick], case.cache_position[pick], case.scale)[0]
+    assert_attention_close(out[pick], want, "beyond the ticket region")
+    assert_attention_close(run_decode(case, 1)[pick], want, "single split, same batch")

@@ -77,7 +77,7 @@ def test_decode_defaults_are_bit_identical(clean_error_word):
     kc, vc = case.k_cache.cuda(), case.v_cache.cuda()
     pt, pos = case.page_table.cuda(), case.cache_position.cuda()
     out = torch.empty_like(q)
-    ws = torch.empty(ops.decode_workspace_bytes(u, case.nq, case.hd, 2), dtype=torch.uint8,
+    ws = torch.zeros(ops.decode_workspace_bytes(u, case.nq, case.hd, 2), dtype=torch.uint8,
                      device="cuda")
     L = _lib.lib()
     rc = L.b200attn_paged_decode(

@@ -51,7 +51,7 @@ def test_static_entry_point_matches_the_allocating_one_twice_in_a_row():
     cases = [_device_case(101, 6, 900), _device_case(202, 9, 2500)]
     outs_static = [torch.zeros_like(c["q"]) for c in cases]
     outs_plain = [torch.zeros_like(c["q"]) for c in cases]
-    workspace = torch.empty(32 << 20, dtype=torch.uint8, device="cuda")
+    workspace = torch.zeros(32 << 20, dtype=torch.uint8, device="cuda")   # counters start at zero
     torch.cuda.synchronize()
     for c, o_s, o_p, splits in zip(cases, outs_static, outs_plain, (4, 7)):
         before = torch.cuda.memory_allocated()

@@ -102,6 +102,7 @@ SIGNATURES = {
          c_int, c_void_p, c_int, c_int, c_int, c_uint64, c_void_p],
     ),
     "b200attn_read_error_word": (c_int, [ctypes.POINTER(c_int32), c_void_p]),
+    "b200attn_peek_error_word_async": (c_int, [c_void_p, c_void_p]),
 }
 
 

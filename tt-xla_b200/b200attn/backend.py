@@ -99,13 +99,19 @@ class B200AttentionMetadataBuilder:
         self.vllm_config = vllm_config
         self.device = device
         self.decode_cur_pos_buffer = None
+        self.error_watch = None
         max_seqs = getattr(getattr(vllm_config, "scheduler_config", None), "max_num_seqs", None)
         if max_seqs and device is not None:
-            self.decode_cur_pos_buffer = torch.zeros(int(max_seqs), dtype=torch.int32,
-                                                     device=device)
+            # -1 = padding row: the decode launch neither streams nor writes anything for it
+            self.decode_cur_pos_buffer = torch.full((int(max_seqs),), -1, dtype=torch.int32,
+                                                    device=device)
+        if device is not None and torch.device(device).type == "cuda":
+            self.error_watch = ops.ErrorWordWatch(torch.device(device))
 
     def build(self, common_prefix_len: int, common_attn_metadata, fast_build: bool = False):
         m = common_attn_metadata
+        if self.error_watch is not None:
+            self.error_watch.poll()      # raises when an earlier step's kernels reported a problem
         qsl = getattr(m, "query_start_loc", None)
         if qsl is None:
             # Same minimal object the reference builder returns.
@@ -163,6 +169,10 @@ def build_varlen_metadata(
         if decode_cur_pos_buffer is not None and decode_cur_pos_buffer.numel() >= num_decodes:
             md.decode_cur_pos = decode_cur_pos_buffer[:num_decodes]
             torch.sub(seq_lens[:num_decodes], 1, out=md.decode_cur_pos)
+            # A CUDA graph captured at a larger (padded) batch reads further into the buffer:
+            # rows past this step's decodes must read as padding, not as an earlier step's
+            # positions.
+            decode_cur_pos_buffer[num_decodes:].fill_(-1)
         else:
             md.decode_cur_pos = (seq_lens[:num_decodes] - 1).contiguous()
     if num_decodes < num_seqs:

@@ -19,6 +19,7 @@ _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 
 CACHE_BF16, CACHE_FP8_E4M3 = 0, 1     # enum b200attn_cache_dtype
+TICKET_BYTES = 65536                  # B200ATTN_DECODE_TICKET_BYTES
 
 
 def _cache_dtype(cache: torch.Tensor) -> int:
@@ -246,13 +247,14 @@ def decode_workspace_bytes(users: int, nq: int, hd: int, splits: int) -> int:
 
 def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
     """Split-KV scratch, cached per (device, stream) and grown on demand.  torch owns the
-    memory; the C library never allocates."""
+    memory; the C library never allocates.  Allocated zeroed: the arrival counters at its start
+    have to be zero on first use (every call leaves them zero)."""
     if nbytes == 0:
         return None
     key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -457,4 +459,52 @@ def read_error_word(device: Optional[torch.device] = None) -> int:
                 ctypes.byref(word), torch.cuda.current_stream(dev).cuda_stream
             ),
         )
+    if word.value:
+        # an aborted launch may have left arrival counters behind: start the scratch afresh
+        for ws in _workspaces.values():
+            if ws.device == dev:
+                ws[:TICKET_BYTES].zero_()
     return int(word.value)
+
+
+class ErrorWordWatch:
+    """Once-per-step watch on the device diagnostics word for a serving loop.  `poll()` raises if
+    an EARLIER poll's asynchronous copy found the word set, then queues the next copy on the
+    current stream; it never synchronises.  A kernel that gave up on a bounded wait (word 1) or
+    met a page id outside the cache (word 2) is therefore reported a step or two later instead
+    of passing silently."""
+
+    MESSAGES = {
+        1: "a bounded wait inside a b200attn kernel ran out (diagnostics word 1): outputs of the "
+           "launches around it are invalid; a row-parallel communicator involved must be rebuilt",
+        2: "a page id or slot outside the KV cache reached a b200attn kernel (diagnostics word 2): "
+           "the access was skipped; the step's metadata is inconsistent with the cache",
+    }
+
+    # called with the word's value before poll() raises (e.g. to switch a fused path off)
+    on_error: list = []
+
+    def __init__(self, device: Optional[torch.device] = None):
+        self.device = device if device is not None else torch.device(
+            "cuda", torch.cuda.current_device())
+        self._host = torch.zeros(1, dtype=torch.int32)
+        if torch.cuda.is_available():
+            self._host = self._host.pin_memory()
+
+    def value(self) -> int:
+        return int(self._host[0])
+
+    def poll(self) -> None:
+        word = self.value()
+        if word:
+            self._host.zero_()
+            for react in list(self.on_error):
+                react(word)
+            if self.device.type == "cuda" and torch.cuda.is_available():
+                read_error_word(self.device)      # clear on the device too
+            raise RuntimeError(self.MESSAGES.get(word, f"device diagnostics word {word}"))
+        _lib.check(
+            "b200attn_peek_error_word_async",
+            _lib.lib().b200attn_peek_error_word_async(
+                self._host.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream),
+        )

@@ -106,12 +106,85 @@ def register() -> None:
 
     register_backend(AttentionBackendEnum.CUSTOM,
                      "b200attn.vllm_plugin.B200VllmAttentionBackend")
-    # o_proj / down_proj through the fused GEMM + all-reduce launch: "1" for every tensor-parallel
-    # size, "0" never, "auto" (default) from four ranks up, where it measured faster end to end
-    # than vLLM's GEMM + all-reduce (two ranks: a tie).
-    mode = os.environ.get("B200ATTN_FUSED_ROW_PARALLEL", "auto")
-    if mode in ("1", "auto"):
-        enable_fused_row_parallel(min_world=2 if mode == "1" else 4)
+    # o_proj / down_proj through the fused GEMM + all-reduce launch is opt-in:
+    # B200ATTN_FUSED_ROW_PARALLEL=1 (every tensor-parallel size) or =4 / =8 (from that many ranks
+    # up).  Unset or 0: vLLM's own GEMM + all-reduce.
+    mode = os.environ.get("B200ATTN_FUSED_ROW_PARALLEL", "0")
+    if mode.isdigit() and int(mode) >= 1:
+        enable_fused_row_parallel(min_world=max(2, int(mode)))
+
+
+def config_allows_fused_row_parallel(vllm_config) -> tuple[bool, str]:
+    """The fused launch is a raw C-ABI call: it is used only where vLLM runs the layer eagerly
+    or inside its own CUDA graphs (compilation mode 0), and only in an engine that selected this
+    repository's attention backend."""
+    if vllm_config is None:
+        return False, "no vLLM config at layer construction"
+    backend = getattr(getattr(vllm_config, "attention_config", None), "backend", None)
+    if getattr(backend, "name", str(backend)) != "CUSTOM":
+        return False, f"attention backend is {backend}, not CUSTOM"
+    mode = getattr(getattr(vllm_config, "compilation_config", None), "mode", None)
+    if int(getattr(mode, "value", mode if mode is not None else -1)) != 0:
+        return False, f"compilation mode {mode}: the launch is not traceable by torch.compile"
+    return True, "ok"
+
+
+def ranks_allow_fused_row_parallel(infos: list, can_access_peer) -> tuple[bool, str]:
+    """`infos`: one dict per tensor-parallel rank (`host`, `device` index, compute capability
+    `major`).  The kernel is sm_100a code, and `cudaIpcOpenMemHandle` plus peer stores need every
+    rank on one node with peer access between every pair of GPUs.  `can_access_peer(i, j)`
+    answers for device indices of this node."""
+    if len(infos) < 2:
+        return False, "a single rank has nothing to reduce"
+    if any(i["major"] != 10 for i in infos):
+        return False, "not every rank runs on compute capability 10.x"
+    if len({i["host"] for i in infos}) != 1:
+        return False, "the tensor-parallel group spans more than one node"
+    devs = [i["device"] for i in infos]
+    if len(set(devs)) != len(devs):
+        return False, "two ranks share one GPU"
+    for a in devs:
+        for b in devs:
+            if a != b and not can_access_peer(a, b):
+                return False, f"GPU {a} cannot access GPU {b} as a peer"
+    return True, "ok"
+
+
+def _agree(group, ok: bool) -> bool:
+    """True only if every rank of `group` says ok (carried as Python objects, any backend)."""
+    import torch.distributed as dist
+
+    votes = [None] * dist.get_world_size(group)
+    dist.all_gather_object(votes, bool(ok), group=group)
+    return all(votes)
+
+
+def create_group_communicator(group, device, max_n: int, max_tokens: int):
+    """Collective over `group`: checks the ranks, creates the communicator, and returns it only
+    if every rank succeeded; otherwise every rank returns None (and keeps vLLM's forward)."""
+    import socket
+
+    import torch.distributed as dist
+
+    from . import tp_linear
+
+    mine = {"host": socket.gethostname(), "device": torch.device(device).index or 0,
+            "major": torch.cuda.get_device_capability(device)[0]}
+    infos = [None] * dist.get_world_size(group)
+    dist.all_gather_object(infos, mine, group=group)
+    ok, _why = ranks_allow_fused_row_parallel(infos, torch.cuda.can_device_access_peer)
+    comm = None
+    if _agree(group, ok):
+        try:
+            comm = tp_linear.RowLinearComm(group, max_n=max_n, max_tokens=max_tokens,
+                                           device=device)
+        except Exception:
+            comm = None
+        if not _agree(group, comm is not None):
+            if comm is not None:
+                comm.close()
+            comm = None
+    return comm
 
 
 def enable_fused_row_parallel(max_tokens: int = 128, max_n: int = 8192, min_world: int = 2) -> None:
@@ -119,36 +192,57 @@ def enable_fused_row_parallel(max_tokens: int = 128, max_n: int = 8192, min_worl
     vllm_tt/vllm_distributed_utils.py:356-363) at the fused GEMM + all-reduce launch for bf16
     batches of up to `max_tokens` rows; every other case keeps vLLM's GEMM + all-reduce.
 
-    The communicator of the tensor-parallel group is created at the first forward of any such
-    layer, which all ranks reach together during vLLM's eager profiling pass, well before decode
-    steps are captured into CUDA graphs.  Layers of groups smaller than `min_world` are left alone."""
-    import torch
+    A layer takes part only if it was built in an engine that selected the CUSTOM attention
+    backend with compilation mode 0 (`config_allows_fused_row_parallel`).  The communicator of the
+    tensor-parallel group is created at the first forward of any such layer, which all ranks
+    reach together during vLLM's eager profiling pass, well before decode steps are captured
+    into CUDA graphs; the ranks first agree that all of them sit on one node with peer access
+    and compute capability 10 (`create_group_communicator`), and fall back together otherwise.
+    When the per-step watch on the diagnostics word reports a problem, the hook switches itself
+    off for the rest of the process.  Layers of groups smaller than `min_world` are left alone."""
+    from vllm.config import get_current_vllm_config_or_none
     from vllm.distributed import get_tp_group
     from vllm.model_executor.layers.linear import RowParallelLinear, UnquantizedLinearMethod
 
-    from . import tp_linear
+    from . import ops, tp_linear
 
     if getattr(RowParallelLinear, "_b200attn_fused", False):
         return
     original = RowParallelLinear.forward
-    state = {"comm": None}
+    original_init = RowParallelLinear.__init__
+    state = {"comm": None, "tried": False, "off": False}
+
+    def switch_off(_word=None):
+        state["off"] = True
+
+    ops.ErrorWordWatch.on_error.append(switch_off)
+
+    def __init__(self, *args, **kwargs):
+        original_init(self, *args, **kwargs)
+        self._b200attn_fusable = config_allows_fused_row_parallel(
+            get_current_vllm_config_or_none())[0]
 
     def forward(self, input_):
         eligible = (
-            self.tp_size >= min_world and self.reduce_results and self.input_is_parallel
+            not state["off"] and getattr(self, "_b200attn_fusable", False)
+            and self.tp_size >= min_world and self.reduce_results and self.input_is_parallel
             and self.bias is None and isinstance(self.quant_method, UnquantizedLinearMethod)
             and input_.dim() == 2 and input_.dtype == torch.bfloat16 and input_.is_cuda
             and self.weight.dtype == torch.bfloat16 and self.weight.shape[0] <= max_n
         )
         if not eligible:
             return original(self, input_)
-        if state["comm"] is None:
-            state["comm"] = tp_linear.RowLinearComm(
-                get_tp_group().cpu_group, max_n=max_n, max_tokens=max_tokens, device=input_.device)
-        if input_.shape[0] == 0 or input_.shape[0] > max_tokens or input_.stride(1) != 1:
+        if not state["tried"]:
+            state["tried"] = True
+            state["comm"] = create_group_communicator(get_tp_group().cpu_group, input_.device,
+                                                      max_n, max_tokens)
+        if (state["comm"] is None or input_.shape[0] == 0 or input_.shape[0] > max_tokens
+                or input_.stride(1) != 1):
             return original(self, input_)
         out = tp_linear.rowlinear_allreduce(input_, self.weight, state["comm"])
         return out if not self.return_bias else (out, None)
 
+    RowParallelLinear.__init__ = __init__
     RowParallelLinear.forward = forward
     RowParallelLinear._b200attn_fused = True
+    RowParallelLinear._b200attn_state = state

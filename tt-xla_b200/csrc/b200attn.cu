@@ -19,6 +19,8 @@
 
 namespace b200attn {
 
+static_assert(kDecTicketBytes == B200ATTN_DECODE_TICKET_BYTES, "header and kernels agree");
+
 // Diagnostics block: code, pad, globaltimer stamp of the latest timeout (see ptx.cuh).
 __device__ __align__(16) int g_err_word[4] = {0, 0, 0, 0};
 
@@ -186,7 +188,7 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   kern<<<grid, kDecThreads, L::kTotalBytes, s>>>(tk, tv, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (p.num_splits > 1) {
+  if (p.num_splits > 1 && !p.tickets) {
     dim3 cgrid(p.num_q_heads, num_users);
     decode_combine_kernel<HD><<<cgrid, HD, 0, s>>>(p);
     e = cudaGetLastError();
@@ -206,7 +208,7 @@ static int launch_decode_fp8(const CUtensorMap& tk, const CUtensorMap& tv, const
   kern<<<grid, kDecThreads, L::kTotalBytes, s>>>(tk, tv, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (p.num_splits > 1) {
+  if (p.num_splits > 1 && !p.tickets) {
     dim3 cgrid(p.num_q_heads, num_users);
     decode_combine_kernel<128><<<cgrid, 128, 0, s>>>(p);
     e = cudaGetLastError();
@@ -498,8 +500,8 @@ int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
   // Cost model fitted to measurements on B200 (times in microseconds):
   //   a CTA needs ~3 us to start streaming; alone on its SM it pulls one 64-token K+V tile
   //   (32 KiB at head_size 128) in ~0.82 us; with `occ` CTAs per SM every CTA gets its share
-  //   of the SM's slice of ~7.2 TB/s; splitting costs a second launch (the combine) and the
-  //   fp32 partial round trip, ~16 us when the kernel is latency-bound.
+  //   of the SM's slice of ~7.2 TB/s; splitting costs the fp32 partial round trip and the merge
+  //   by the last split to arrive, ~4 us.
   const double tile_bytes = 2.0 * kDecTile * head_size * 2.0;
   const double bw_per_sm = 7.2e6 / sm;                       // bytes per us
   const int occ = head_size > 64 ? 2 : 3;                    // resident CTAs per SM
@@ -524,7 +526,7 @@ int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
       const double cta = 3.0 + chunk * (occ * tile_bytes / bw_per_sm);
       t = ctas * cta / slots + 0.5 * cta;    // work-conserving waves + half a CTA as tail (ragged batches)
     }
-    if (s > 1) t += 16.0;
+    if (s > 1) t += 4.0;
     if (s == 1 || t < best_t * 0.99) {
       best_t = t;
       best_s = s;
@@ -539,7 +541,7 @@ size_t b200attn_decode_workspace_bytes(int num_users, int num_q_heads, int head_
   const size_t rows = static_cast<size_t>(num_users) * num_q_heads * num_splits;
   size_t o_bytes = rows * head_size * sizeof(float);
   o_bytes = (o_bytes + 255) & ~static_cast<size_t>(255);
-  return o_bytes + rows * sizeof(float2);
+  return kDecTicketBytes + o_bytes + rows * sizeof(float2);
 }
 
 
@@ -601,6 +603,7 @@ int b200attn_paged_decode_step(void* out, int64_t out_row_stride, const void* q,
     return B200ATTN_ERR_NULL_POINTER;
   if (num_users < 0 || num_q_heads <= 0 || page_table_width <= 0 || num_splits < 0)
     return B200ATTN_ERR_BAD_ARGUMENT;
+  if (num_splits > kDecMaxSplits) return B200ATTN_ERR_TOO_LARGE;
   if (int rc = check_cache_geometry(num_kv_heads, head_size, block_size, num_blocks)) return rc;
   if (num_q_heads % num_kv_heads != 0) return B200ATTN_ERR_BAD_ARGUMENT;
   const int group = num_q_heads / num_kv_heads;
@@ -664,8 +667,14 @@ int b200attn_paged_decode_step(void* out, int64_t out_row_stride, const void* q,
     const size_t rows_p = static_cast<size_t>(num_users) * num_q_heads * num_splits;
     size_t o_bytes = rows_p * head_size * sizeof(float);
     o_bytes = (o_bytes + 255) & ~static_cast<size_t>(255);
-    p.part_o = static_cast<float*>(workspace);
-    p.part_ml = reinterpret_cast<float2*>(static_cast<uint8_t*>(workspace) + o_bytes);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    // One arrival counter per (user, KV head) when they fit the ticket region: the last split
+    // to arrive merges the partials inside the same launch.  Larger batches fall back to the
+    // separate combine launch.
+    if (static_cast<size_t>(num_users) * num_kv_heads * sizeof(unsigned int) <= kDecTicketBytes)
+      p.tickets = reinterpret_cast<unsigned int*>(ws);
+    p.part_o = reinterpret_cast<float*>(ws + kDecTicketBytes);
+    p.part_ml = reinterpret_cast<float2*>(ws + kDecTicketBytes + o_bytes);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (fp8)
@@ -819,6 +828,14 @@ int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* 
     }
     ws = g_static_workspace_addr[dev];
   }
+  // The arrival counters this call uses must start at zero whatever an earlier (possibly
+  // aborted) call left behind.
+  if (num_splits > 1 && num_users > 0) {
+    size_t n = static_cast<size_t>(num_users) * num_kv_heads * sizeof(unsigned int);
+    if (n > kDecTicketBytes) n = kDecTicketBytes;
+    cudaError_t e = cudaMemsetAsync(ws, 0, n, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   return b200attn_paged_decode(out, out_row_stride, q, q_row_stride, k_cache, v_cache,
                                page_table, page_table_stride, page_table_width, cur_pos,
                                num_users, num_q_heads, num_kv_heads, head_size, block_size,
@@ -835,6 +852,15 @@ int b200attn_read_error_word(int32_t* out_host, void* stream) {
   if (e == cudaSuccess) e = cudaMemsetAsync(dev->err_word, 0, sizeof(int), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   return static_cast<int>(e);
+}
+
+int b200attn_peek_error_word_async(int32_t* out_pinned_host, void* stream) {
+  if (!out_pinned_host) return B200ATTN_ERR_NULL_POINTER;
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  return static_cast<int>(cudaMemcpyAsync(out_pinned_host, dev->err_word, sizeof(int),
+                                          cudaMemcpyDeviceToHost,
+                                          static_cast<cudaStream_t>(stream)));
 }
 
 // ------------------------------------------------------------------------------ row-parallel
@@ -974,7 +1000,7 @@ int b200attn_rowlinear_allreduce(void* out, int64_t out_row_stride, const void* 
   p.world = world;
   p.src_stride = world > 1 ? rl_area_bytes(max_tokens, max_n) : 0;
   p.two_shot = reduce_mode == 0 ? (world > 2) : (reduce_mode == 2);
-  p.peer_timeout_ns = peer_timeout_ns ? peer_timeout_ns : 10ull * 1000 * 1000 * 1000;
+  p.peer_timeout_ns = peer_timeout_ns ? peer_timeout_ns : 1000ull * 1000 * 1000;
   p.err_word = dev->err_word;
   const int nb = rl_token_rows(num_tokens);
   CUtensorMap tw, tx;

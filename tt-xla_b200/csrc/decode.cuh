@@ -9,7 +9,8 @@
 // kernel is HBM-bound; tensor throughput is irrelevant), the softmax is the online
 // (running max / running sum) form in fp32 with warp-shuffle row reductions.  The four
 // warps' partial (m, l, O) are merged through shared memory at the end, and the CTA writes
-// either the final bf16 rows (one split) or an fp32 partial that the combine kernel merges.
+// either the final bf16 rows (one split) or an fp32 partial; the split that finishes last for a
+// (user, KV head) merges the partials (decode_split_finish), so one launch does it all.
 #pragma once
 #include "kv_scatter.cuh"
 #include "ptx.cuh"
@@ -31,6 +32,8 @@ struct DecodeParams {
   const int32_t* cur_pos;
   float* part_o;    // [users, nq, splits, hd]
   float2* part_ml;  // [users, nq, splits]  (running max in log2 units, running sum)
+  unsigned int* tickets;   // [users, nkv] arrival counters of the splits, zero between launches;
+                           // NULL: the partials are merged by decode_combine_kernel instead
   int num_q_heads;
   int num_kv_heads;
   int group;        // nq / nkv
@@ -100,6 +103,95 @@ __device__ __forceinline__ float apply_sink(float& m, float& l, float sink_log2)
   return f;
 }
 
+constexpr int kDecMaxSplits = 256;       // bounds the merge scratch in shared memory
+constexpr int kDecTicketBytes = 65536;   // ticket region at the start of the split-KV workspace
+
+// End of a split's work when the launch has more than one split: the split's partial (max, sum,
+// O) for the G query heads is already in global memory.  The split takes a ticket of its
+// (user, KV head); whoever arrives last finds every other partial published (each writer fences
+// before its ticket), merges them and writes the bf16 rows.  Nobody waits for anybody, so
+// nothing can hang, and no second launch is needed.  Called by the kDecConsumerWarps * 32
+// threads `tid` = 0..127 with `scratch` = free shared memory of (32 * splits + 40) floats.
+template <int HD>
+__device__ __forceinline__ void decode_split_finish(const DecodeParams& p, int user, int kvh,
+                                                    float* scratch, int tid) {
+  constexpr int kThreads = kDecConsumerWarps * 32;
+  const int S = p.num_splits;
+  const int G = p.group;
+  float* fac = scratch;                    // [G][S] running max of a split, then its merge factor
+  float* sl = scratch + 16 * S;            // [G][S] running sum of a split
+  float* row_m = sl + 16 * S;              // [G] merged max
+  float* row_l = row_m + 16;               // [G] merged sum
+  volatile int* last_flag = reinterpret_cast<volatile int*>(row_l + 16);
+  unsigned int* ticket = p.tickets + static_cast<int64_t>(user) * p.num_kv_heads + kvh;
+
+  __threadfence();                         // this thread's partial stores, device-wide
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+  if (tid == 0) *last_flag = atomicAdd(ticket, 1u) == static_cast<unsigned int>(S - 1);
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+  if (!*last_flag) return;
+  __threadfence();
+
+  const int64_t row0 = (static_cast<int64_t>(user) * p.num_q_heads + kvh * G) * S;
+  for (int i = tid; i < G * S; i += kThreads) {
+    const float2 ml = __ldcg(p.part_ml + row0 + i);
+    fac[i] = ml.x;
+    sl[i] = ml.y;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int r = warp; r < G; r += kDecConsumerWarps) {
+    float m = -INFINITY;
+    for (int s = lane; s < S; s += 32) m = fmaxf(m, fac[r * S + s]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.f;
+    for (int s = lane; s < S; s += 32) {
+      const float ms = fac[r * S + s];
+      const float f = (ms == -INFINITY) ? 0.f : fast_exp2(ms - m);   // empty splits carry -inf
+      fac[r * S + s] = f;
+      l += f * sl[r * S + s];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) {
+      row_m[r] = m;
+      row_l[r] = l;
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+  for (int i = tid; i < G * HD; i += kThreads) {
+    const int r = i / HD, d = i - r * HD;
+    const float* src = p.part_o + (row0 + static_cast<int64_t>(r) * S) * HD + d;
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 4 <= S; s += 4) {
+      // an empty split published no O rows: its factor is 0 and its memory must not be read
+      // into the sum (0 * garbage may be NaN)
+      const float f0 = fac[r * S + s], f1 = fac[r * S + s + 1];
+      const float f2 = fac[r * S + s + 2], f3 = fac[r * S + s + 3];
+      const float x0 = f0 != 0.f ? __ldcg(src + static_cast<int64_t>(s) * HD) : 0.f;
+      const float x1 = f1 != 0.f ? __ldcg(src + static_cast<int64_t>(s + 1) * HD) : 0.f;
+      const float x2 = f2 != 0.f ? __ldcg(src + static_cast<int64_t>(s + 2) * HD) : 0.f;
+      const float x3 = f3 != 0.f ? __ldcg(src + static_cast<int64_t>(s + 3) * HD) : 0.f;
+      acc += f0 * x0;
+      acc += f1 * x1;
+      acc += f2 * x2;
+      acc += f3 * x3;
+    }
+    for (; s < S; ++s) {
+      const float f = fac[r * S + s];
+      if (f != 0.f) acc += f * __ldcg(src + static_cast<int64_t>(s) * HD);
+    }
+    float m = row_m[r], l = row_l[r];
+    const int head = kvh * G + r;
+    if (p.sinks) acc *= apply_sink(m, l, p.sinks[head] * 1.4426950408889634f);
+    p.out[static_cast<int64_t>(user) * p.out_row_stride + head * HD + d] =
+        __float2bfloat16(l > 0.f ? acc / l : 0.f);
+  }
+  if (tid == 0) *ticket = 0u;              // leave the counter as the next launch expects it
+}
+
 template <int HD, int BS, int STAGES>
 struct DecodeSmem {
   static constexpr int kSub = HD / 64;                 // 64-element (128 B) column groups
@@ -153,6 +245,8 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
                                 p.num_splits + split;
         p.part_ml[row] = make_float2(-INFINITY, 0.f);
       }
+      if (p.tickets && threadIdx.x < kDecConsumerWarps * 32)
+        decode_split_finish<HD>(p, user, kvh, reinterpret_cast<float*>(ring), threadIdx.x);
     } else {
       for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
         const int r = i / HD, d = i - r * HD;
@@ -430,6 +524,8 @@ paged_decode_splitkv_kernel(const __grid_constant__ CUtensorMap tm_k,
       if (d == 0) p.part_ml[row] = make_float2(m, l);
     }
   }
+  if (p.num_splits > 1 && p.tickets)
+    decode_split_finish<HD>(p, user, kvh, reinterpret_cast<float*>(ring), threadIdx.x);
 }
 
 // Merges the split partials of one (user, q head) row and writes bf16.

@@ -106,6 +106,8 @@ paged_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_k,
                                 p.num_splits + split;
         p.part_ml[row] = make_float2(-INFINITY, 0.f);
       }
+      if (p.tickets && threadIdx.x < kDecConsumerWarps * 32)
+        decode_split_finish<HD>(p, user, kvh, reinterpret_cast<float*>(ring), threadIdx.x);
     } else {
       for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
         const int r = i / HD, d = i - r * HD;
@@ -393,6 +395,8 @@ paged_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_k,
       if (d == 0) p.part_ml[row] = make_float2(m, l);
     }
   }
+  if (p.num_splits > 1 && p.tickets)
+    decode_split_finish<HD>(p, user, kvh, reinterpret_cast<float*>(ring), threadIdx.x);
 }
 
 }  // namespace b200attn
