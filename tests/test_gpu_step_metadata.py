@@ -76,3 +76,41 @@ def test_decode_step_driven_by_device_built_metadata(clean_error_word):
     assert torch.equal(got_k[1:], want_k[1:]) and torch.equal(got_v[1:], want_v[1:])
     assert_attention_close(out[:n], want_out, "decode via device-built metadata")
     assert out[n:].abs().sum().item() == 0
+
+
+def test_device_step_state_drives_two_steps_on_the_same_buffers(clean_error_word):
+    """The product path of the builder: scheduler state on the device, one launch per step into
+    persistent buffers, the Impl's forward on the result; two steps in a row (the second one
+    more token into every context)."""
+    from b200attn import B200AttentionBackendImpl, B200AttentionMetadataBuilder
+
+    g = torch.Generator().manual_seed(15)
+    nq, nkv, hd, bs, n, rows, width = 8, 2, 64, 32, 5, 8, 10
+    bt = (torch.randperm(n * width, generator=g) + 1).reshape(n, width).int()
+    computed = torch.randint(1, width * bs - 3, (n,), generator=g).int()
+    sched = torch.ones(n, dtype=torch.int32)
+    nb = n * width + 1
+    kc, vc = randn_bf16((nb, nkv, bs, hd), g), randn_bf16((nb, nkv, bs, hd), g)
+    state = B200AttentionMetadataBuilder(device=torch.device("cuda")).device_step_state(
+        rows, width, bs, tokens_per_row=1)
+    impl = B200AttentionBackendImpl(nq, hd, hd ** -0.5, nkv, None, None, "auto")
+    kv = [kc.cuda(), vc.cuda()]
+    d_computed, d_sched, d_bt = computed.cuda(), sched.cuda(), bt.cuda()
+    ptrs = None
+    for step in range(2):
+        q, k, v = (randn_bf16((rows, h * hd), g) for h in (nq, nkv, nkv))
+        meta = state.build(d_computed, d_sched, d_bt)
+        now = (meta.cache_position.data_ptr(), meta.page_table.data_ptr())
+        assert ptrs is None or now == ptrs           # same buffers every step
+        ptrs = now
+        out = torch.empty(rows, nq * hd, dtype=torch.bfloat16, device="cuda")
+        impl.forward(None, q.cuda(), k.cuda(), v.cuda(), kv, meta, output=out)
+        want_out, kc, vc = restate.impl_forward(
+            q[:n], k[:n], v[:n], kc, vc, num_heads=nq, num_kv_heads=nkv, head_size=hd,
+            scale=hd ** -0.5, num_users=n, cache_position=computed + sched - 1, page_table=bt,
+            compute_dtype=torch.float32)
+        assert torch.equal(kv[0].cpu()[1:], kc[1:]) and torch.equal(kv[1].cpu()[1:], vc[1:])
+        assert_attention_close(out[:n], want_out, f"step {step}")
+        assert out[n:].abs().sum().item() == 0
+        computed = computed + 1
+        d_computed += 1

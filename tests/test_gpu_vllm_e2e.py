@@ -44,6 +44,8 @@ def runs(tmp_path_factory):
     pytest.importorskip("vllm")
     pytest.importorskip("transformers")
     workdir = str(tmp_path_factory.mktemp("vllm_e2e"))
+    subprocess.run([sys.executable, WORKER, "--prepare", "--workdir", workdir], check=True,
+                   stdin=subprocess.DEVNULL, capture_output=True, timeout=600)
     return run_worker("custom", workdir), run_worker("stock", workdir)
 
 

@@ -3,7 +3,12 @@
 attention backend (registered as CUSTOM, the enum member the reference plugin registers) or
 vLLM's stock backend, and writes greedy tokens and log-probabilities to a JSON file.
 
+    python tiny_llama_worker.py --prepare --workdir DIR          (writes the checkpoint, once)
     python tiny_llama_worker.py --backend custom|stock --out result.json --workdir DIR
+
+The checkpoint is written by a process of its own: vLLM forks its engine process, and a fork
+after this process has run multi-threaded CPU kernels (the weight initialisation) leaves the
+child with a dead thread pool.
 """
 import argparse
 import json
@@ -34,21 +39,27 @@ def make_checkpoint(path: str) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--backend", choices=["custom", "stock"], required=True)
-    ap.add_argument("--out", required=True)
+    ap.add_argument("--backend", choices=["custom", "stock"])
+    ap.add_argument("--out")
     ap.add_argument("--workdir", required=True)
     ap.add_argument("--kv-cache-dtype", default="auto")
+    ap.add_argument("--prepare", action="store_true")
     args = ap.parse_args()
+    model_dir = os.path.join(args.workdir, "tiny_llama")
+    if args.prepare:
+        make_checkpoint(model_dir)
+        return
+    assert args.backend and args.out, "--backend and --out are required"
+    assert os.path.exists(os.path.join(model_dir, "config.json")), "run with --prepare first"
 
     # engine-core child processes find the plugin's entry point through PYTHONPATH
     os.environ["PYTHONPATH"] = PKG + os.pathsep + os.environ.get("PYTHONPATH", "")
     os.environ["B200ATTN_FUSED_ROW_PARALLEL"] = "0"
+    os.environ.setdefault("VLLM_WORKER_MULTIPROC_METHOD", "spawn")
     sys.path.insert(0, PKG)
     import torch
     from vllm import LLM, SamplingParams
 
-    model_dir = os.path.join(args.workdir, "tiny_llama")
-    make_checkpoint(model_dir)
     kw = dict(model=model_dir, skip_tokenizer_init=True, dtype="bfloat16", block_size=64,
               max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=256,
               enable_chunked_prefill=True, gpu_memory_utilization=0.25, seed=0,

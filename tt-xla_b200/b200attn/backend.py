@@ -108,6 +108,12 @@ class B200AttentionMetadataBuilder:
         if device is not None and torch.device(device).type == "cuda":
             self.error_watch = ops.ErrorWordWatch(torch.device(device))
 
+    def device_step_state(self, rows: int, page_table_width: int, block_size: int,
+                          tokens_per_row: int = 1) -> "DeviceStepState":
+        """For runners that hold their scheduler state on the GPU: the one-launch metadata build
+        (see DeviceStepState)."""
+        return DeviceStepState(rows, page_table_width, block_size, tokens_per_row, self.device)
+
     def build(self, common_prefix_len: int, common_attn_metadata, fast_build: bool = False):
         m = common_attn_metadata
         if self.error_watch is not None:
@@ -129,6 +135,44 @@ class B200AttentionMetadataBuilder:
             is_causal=getattr(m, "causal", True),
             decode_cur_pos_buffer=self.decode_cur_pos_buffer,
         )
+
+
+class DeviceStepState:
+    """Persistent device buffers of the plugin-form metadata for a runner that keeps its
+    scheduler state (`num_computed`, `num_scheduled`, `block_table`) on the GPU.  `build()` fills
+    them with ONE launch (`b200attn_build_step_metadata`) and returns the B200Metadata every layer
+    of the step receives: what `TTModelRunner._prepare_inputs` computes on the host and copies
+    over tensor by tensor (model_runner.py:1722-1741, 1945-1993).  The buffers keep their
+    addresses, so a step captured into a CUDA graph replays against the next step's values."""
+
+    def __init__(self, rows: int, page_table_width: int, block_size: int, tokens_per_row: int,
+                 device):
+        from . import metadata as _md
+
+        self.rows, self.block_size, self.tokens_per_row = rows, block_size, tokens_per_row
+        fill_width = _md.fill_page_table_width(tokens_per_row, block_size, page_table_width)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.buffers = _md.StepMetadata(
+            cache_position=torch.full((rows,), -1, **i32),
+            page_table=torch.zeros((rows, page_table_width), **i32),
+            fill_page_table=torch.zeros((rows, fill_width), **i32),
+            slot_mapping=torch.full((rows * tokens_per_row,), -1, dtype=torch.int64,
+                                    device=device),
+            chunk_start_idx=None)
+        self.batch_idx = torch.arange(rows, **i32)
+
+    def build(self, num_computed: torch.Tensor, num_scheduled: torch.Tensor,
+              block_table: torch.Tensor, chunk_start_idx: Optional[torch.Tensor] = None,
+              max_seq_len: int = 0) -> "B200Metadata":
+        from . import metadata as _md
+
+        _md.build_step_metadata(num_computed, num_scheduled, block_table, self.block_size,
+                                self.buffers, self.tokens_per_row)
+        b = self.buffers
+        return B200Metadata(cache_position=b.cache_position, page_table=b.page_table,
+                            fill_page_table=b.fill_page_table, batch_idx=self.batch_idx,
+                            chunk_start_idx=chunk_start_idx, num_users=self.rows,
+                            slot_mapping=b.slot_mapping, max_seq_len=max_seq_len)
 
 
 def build_varlen_metadata(

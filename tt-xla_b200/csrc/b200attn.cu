@@ -497,37 +497,31 @@ int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
   int sm = 148;
   DeviceInfo* dev;
   if (get_device(&dev) == B200ATTN_OK) sm = dev->sm_count;
-  // Cost model fitted to measurements on B200 (times in microseconds):
-  //   a CTA needs ~3 us to start streaming; alone on its SM it pulls one 64-token K+V tile
-  //   (32 KiB at head_size 128) in ~0.82 us; with `occ` CTAs per SM every CTA gets its share
-  //   of the SM's slice of ~7.2 TB/s; splitting costs the fp32 partial round trip and the merge
-  //   by the last split to arrive, ~4 us.
+  // Cost model fitted to a sweep of split counts on B200 (20 batch shapes, times in
+  // microseconds).  A launch costs ~6 us whatever it does; a CTA alone on its SM streams one
+  // 64-token K+V tile (32 KiB at head_size 128) in ~0.54 us, and all CTAs together share
+  // ~7.0 TB/s; the end of a launch is ragged in proportion to the longest CTA (a quarter of its
+  // streaming time); CTAs beyond the resident set cost ~6 us per extra wave of start-up; more
+  // than one split costs ~2 us for the merge by the last split to arrive plus ~0.1 us per split.
   const double tile_bytes = 2.0 * kDecTile * head_size * 2.0;
-  const double bw_per_sm = 7.2e6 / sm;                       // bytes per us
+  const double bw = 7.0e6;                                   // bytes per us
   const int occ = head_size > 64 ? 2 : 3;                    // resident CTAs per SM
-  const double t_alone = 0.82 * tile_bytes / 32768.0;
+  const double t_alone = 0.54 * tile_bytes / 32768.0;
   const int64_t tiles = (max_context_len + kDecTile - 1) / kDecTile;
   const int64_t base = static_cast<int64_t>(num_users) * num_kv_heads;
-  const int64_t slots = static_cast<int64_t>(occ) * sm;
+  const double slots = static_cast<double>(occ) * sm;
   const int max_s = static_cast<int>(tiles < 128 ? tiles : 128);
   int best_s = 1;
   double best_t = 0.0;
   for (int s = 1; s <= max_s; ++s) {
     const int64_t chunk = (tiles + s - 1) / s;
-    const int64_t ctas = base * s;
-    double t;
-    if (ctas <= slots) {
-      const int64_t per_sm = (ctas + sm - 1) / sm;
-      const double t_tile = per_sm <= 1 ? t_alone
-                                        : (per_sm * tile_bytes / bw_per_sm > t_alone
-                                               ? per_sm * tile_bytes / bw_per_sm : t_alone);
-      t = 3.0 + chunk * t_tile;
-    } else {
-      const double cta = 3.0 + chunk * (occ * tile_bytes / bw_per_sm);
-      t = ctas * cta / slots + 0.5 * cta;    // work-conserving waves + half a CTA as tail (ragged batches)
-    }
-    if (s > 1) t += 4.0;
-    if (s == 1 || t < best_t * 0.99) {
+    const double ctas = static_cast<double>(base) * s;
+    const double shared = ctas * chunk * tile_bytes / bw;
+    const double alone = chunk * t_alone;
+    double t = 6.0 + (shared > alone ? shared : alone) + 0.25 * alone;
+    if (s > 1) t += 2.0 + 0.1 * s;
+    if (ctas > slots) t += 6.0 * (ctas / slots - 1.0);
+    if (s == 1 || t < best_t * 0.995) {
       best_t = t;
       best_s = s;
     }

@@ -1,25 +1,32 @@
 // Causal varlen / chunked prefill attention on tcgen05 tensor cores.
 //
-// Persistent kernel: one CTA per SM walks a list of work items; an item is 2 x 128 query
-// rows (tiles A and B) of one sequence x one query head.  KV is consumed in tiles of 128
-// keys, shared by both query tiles.  Ten warps:
-//   warp 0      TMA producer: per item Q_A and Q_B, then K_0, V_0, K_1, V_1, ... into a ring
-//               of swizzled [128 rows x 128 B] sub-tiles (paged source: one box per page;
-//               fresh source: one box per 64-wide column group).  It runs ahead of the other
-//               warps, so the loads of the next item overlap the tail of the current one.
-//   warp 1      allocates tensor memory once (S_A, S_B, O_A, O_B = 512 columns) and issues
-//               tcgen05.mma from one lane in the order
-//                   PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...
-//               so that the tensor pipe works for one query tile while the other tile's
-//               softmax runs; at an item boundary it goes straight on to QK(0) of the next
-//               item while the softmax warps are still in their epilogue.
-//   warps 2-5   softmax warpgroup of tile A, warps 6-9 of tile B; one thread per query row:
-//               tcgen05.ld the row of S, causal mask on diagonal tiles, running max with a
-//               lazy rescale threshold, ex2 via packed fp32 FMA, row sum, P as packed bf16 back
-//               into tensor memory over the first 64 columns of its S buffer (the PV MMA takes
-//               its A operand from tensor memory); rescales its O row in tensor memory when the
-//               running max moved; per item it normalises O by 1/l and stores bf16.
-// Items are ordered heaviest first (by the index of the 256-row block inside its sequence,
+// Persistent kernel: one CTA per SM walks a list of work items; an item is 128 query rows of
+// one sequence x one query head.  KV is consumed in tiles of 128 keys.  Four warpgroups:
+//   warpgroup 0   warp 0: TMA producer: per item the Q tile (two Q buffers, so the next item's
+//                 Q lands while this one is still in use), then K_0, V_0, K_1, V_1, ... into a
+//                 ring of swizzled [128 rows x 128 B] sub-tiles (paged source: one box per page;
+//                 fresh source: one box per 64-wide column group).
+//                 warp 1: allocates tensor memory once (S_0, S_1, O_0, O_1 = 512 columns) and
+//                 issues tcgen05.mma from one lane.  S is double-buffered by KV tile, so
+//                 QK(t+1) is issued BEFORE the softmax of tile t has produced P(t):
+//                     QK(t+1), [wait P(t)] PV(t), QK(t+2), [wait P(t+1)] PV(t+1), ...
+//                 the tile counter t runs on across items, so the first QK of the next item is
+//                 in flight while the last tiles of this one are still in their softmax.
+//                 O is double-buffered by item, so the next item accumulates while the epilogue
+//                 warpgroup reads this one out.
+//   warpgroups 1, 2   softmax of the even / odd tiles, one thread per query row: tcgen05.ld the
+//                 row of S, causal mask on the diagonal tile, row max; the running max of a row
+//                 is handed from tile to tile through shared memory (the only serial link
+//                 between the two warpgroups: a tile's exponentials need the max of the tile
+//                 before, nothing else of it, so the exponentials of consecutive tiles overlap);
+//                 ex2 via packed fp32 FMA, row sum kept per warpgroup, P as packed bf16 back into
+//                 tensor memory over the first 64 columns of its S buffer (the PV MMA takes its A
+//                 operand from tensor memory); rescales the O row in tensor memory in the rare
+//                 case that the running max moved by more than a threshold.
+//   warpgroup 3   epilogue: per item, waits for the last PV, merges the two warpgroups' row
+//                 sums, normalises O by 1/l and stores bf16 rows; hands O back at once.
+// Registers follow the roles (setmaxnreg): the two softmax warpgroups hold a whole S row each.
+// Items are ordered heaviest first (by the index of the 128-row block inside its sequence,
 // highest first, heads of one block adjacent) and dealt to the CTAs in rounds of alternating
 // direction (0..G-1, G-1..0, ...), which evens out the per-CTA sums of a sorted list.
 // Every mbarrier wait is bounded; tensor memory is always freed before exit.
@@ -28,15 +35,18 @@
 
 namespace b200attn {
 
-constexpr int kPfM = 128;        // query rows per tile
-constexpr int kPfQTiles = 2;     // query tiles per item
-constexpr int kPfRowsPerItem = kPfM * kPfQTiles;
+constexpr int kPfM = 128;        // query rows per item
+constexpr int kPfRowsPerItem = kPfM;
 constexpr int kPfN = 128;        // keys per KV tile
-constexpr int kPfThreads = 320;
+constexpr int kPfThreads = 512;  // four warpgroups
 constexpr float kPfRescaleThreshold = 8.f;  // log2 units
-constexpr int kPfSeqCache = 2048;           // sequences whose cu_q is cached in shared memory
+constexpr int kPfSeqCache = 1024;           // sequences whose cu_q is cached in shared memory
 constexpr int kPfLevelOrderMaxSeqs = 64;    // above this, items keep plain sequence order
-constexpr int kPfItemTable = 96;            // rounds whose item is decoded once, up front
+constexpr int kPfItemTable = 128;           // rounds whose item is decoded once, up front
+// register budgets per warpgroup (sum = 4 x 128, the per-thread budget the kernel launches with)
+constexpr int kPfRegsProducer = 88;
+constexpr int kPfRegsSoftmax = 184;
+constexpr int kPfRegsEpilogue = 56;
 
 struct PrefillParams {
   __nv_bfloat16* out;
@@ -64,12 +74,16 @@ struct PrefillSmem {
   static constexpr int kSubBytes = 128 * 128;             // 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;     // one Q, K or V tile
   static constexpr int kSlots = (HD == 128) ? 4 : 8;      // ring slots (one K or V tile each)
-  static constexpr int kQOff = 0;
-  static constexpr int kRingOff = kPfQTiles * kTileBytes;
+  static constexpr int kQOff = 0;                         // two Q buffers (by item parity)
+  static constexpr int kRingOff = 2 * kTileBytes;
   static constexpr int kSeqOff = kRingOff + kSlots * kTileBytes;
   static constexpr int kItemOff = kSeqOff + (kPfSeqCache + 4) * 4;   // keeps 16-byte alignment
-  static constexpr int kBarOff = kItemOff + kPfItemTable * 16;
-  static constexpr int kNumBars = 2 + 2 * kSlots + 4 * kPfQTiles;
+  static constexpr int kMaxOff = kItemOff + kPfItemTable * 16;       // running max [tile parity][row]
+  static constexpr int kStatOff = kMaxOff + 2 * kPfM * 4;            // (max, sum) [item parity][group][row]
+  static constexpr int kBarOff = kStatOff + 2 * 2 * kPfM * 8;
+  // q_full[2] q_empty[2] full[kSlots] empty[kSlots] s_full[2] p_full[2] pv_done[2] m_ready[2]
+  // o_full[2] o_empty[2] stat_full[2] stat_empty[2]
+  static constexpr int kNumBars = 4 + 2 * kSlots + 16;
   static constexpr int kTotalBytes = kBarOff + kNumBars * 8 + 16 + 1024;
   static_assert(kItemOff % 16 == 0, "16-byte vector access alignment");
   static_assert(kBarOff % 8 == 0, "barrier alignment");
@@ -87,14 +101,13 @@ struct PrefillItemKey {
 // What every role needs to know about one work item.
 struct PrefillItem {
   int seq, head, q0, seq_q_begin, seq_len_q, start;
-  int rows_valid[kPfQTiles], first_pos[kPfQTiles];
-  // KV tiles are counted relative to the item's first tile j0 (0 without a sliding window):
-  // query tile w works on relative tiles skip[w] .. n_rel[w]-1.
-  int j0, skip[kPfQTiles], n_rel[kPfQTiles];
-  int n_max;          // relative tiles of the item (the larger n_rel)
+  int rows_valid;     // query rows of the item that exist (the last block of a sequence is ragged)
+  int first_pos;      // absolute position of the item's first query row
+  int j0;             // first KV tile any row attends (0 without a sliding window)
+  int n_tiles;        // KV tiles j0 .. j0 + n_tiles - 1
 };
 
-// Item index -> (sequence, 256-row block, head).  `cu` is cu_q (shared-memory copy when the
+// Item index -> (sequence, 128-row block, head).  `cu` is cu_q (shared-memory copy when the
 // batch fits the cache).  Heaviest first: blocks ranked by their index inside their sequence,
 // highest first across sequences; the heads of one block are adjacent.  The search costs
 // microseconds, so the kernel runs it once per round up front (one thread per round) and the
@@ -161,30 +174,28 @@ __device__ __forceinline__ bool prefill_expand_item(const PrefillParams& p,
   it.start = key.start;
   it.seq_q_begin = cu[key.seq];
   it.seq_len_q = cu[key.seq + 1] - it.seq_q_begin;
-#pragma unroll
-  for (int w = 0; w < kPfQTiles; ++w) {
-    it.rows_valid[w] = max(0, min(kPfM, it.seq_len_q - it.q0 - w * kPfM));
-    it.first_pos[w] = it.start + it.q0 + w * kPfM;
-  }
-  // first key any row of tile A may attend (tile A starts lowest)
-  const int lo = (p.window > 0 && it.first_pos[0] + 1 > p.window) ? it.first_pos[0] + 1 - p.window : 0;
+  it.rows_valid = max(0, min(kPfM, it.seq_len_q - it.q0));
+  it.first_pos = it.start + it.q0;
+  // first key the first row may attend (it starts lowest)
+  const int lo = (p.window > 0 && it.first_pos + 1 > p.window) ? it.first_pos + 1 - p.window : 0;
   it.j0 = lo / kPfN;
-#pragma unroll
-  for (int w = 0; w < kPfQTiles; ++w) {
-    const int n_abs =
-        it.rows_valid[w] > 0 ? (it.first_pos[w] + it.rows_valid[w] - 1) / kPfN + 1 : 0;
-    const int lo_w =
-        (p.window > 0 && it.first_pos[w] + 1 > p.window) ? it.first_pos[w] + 1 - p.window : 0;
-    it.n_rel[w] = n_abs > 0 ? n_abs - it.j0 : 0;
-    it.skip[w] = n_abs > 0 ? lo_w / kPfN - it.j0 : 0;
-  }
-  it.n_max = max(it.n_rel[0], it.n_rel[1]);   // tile A never ends later than tile B
-  return true;
+  const int n_abs = it.rows_valid > 0 ? (it.first_pos + it.rows_valid - 1) / kPfN + 1 : 0;
+  it.n_tiles = n_abs - it.j0;
+  return it.n_tiles > 0;
 }
 
 // Item handled by CTA `cta` of `num_ctas` in round `round` (alternating direction per round).
 __device__ __forceinline__ int prefill_item_of(int round, int cta, int num_ctas) {
   return round * num_ctas + ((round & 1) ? (num_ctas - 1 - cta) : cta);
+}
+
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 template <int HD, int BS, bool WIN>
@@ -203,20 +214,27 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint8_t* ring = smem + L::kRingOff;
   int32_t* cu_smem = reinterpret_cast<int32_t*>(smem + L::kSeqOff);
   PrefillItemKey* item_table = reinterpret_cast<PrefillItemKey*>(smem + L::kItemOff);
+  float* m_sh = reinterpret_cast<float*>(smem + L::kMaxOff);          // [tile parity][row]
+  float2* stat_sh = reinterpret_cast<float2*>(smem + L::kStatOff);    // [item parity][group][row]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* q_full = bars;                   // Q tiles of the item landed (TMA -> MMA)
-  uint64_t* q_empty = bars + 1;              // last QK of the item retired (MMA -> TMA)
-  uint64_t* full = bars + 2;                 // [kSlots]
+  uint64_t* q_full = bars;                   // [2] Q of the item landed (TMA -> MMA)
+  uint64_t* q_empty = bars + 2;              // [2] last QK of the item retired (MMA -> TMA)
+  uint64_t* full = bars + 4;                 // [kSlots]
   uint64_t* empty = full + kSlots;           // [kSlots]
-  uint64_t* s_full = empty + kSlots;         // [2]  S of tile A / B ready (MMA -> softmax)
-  uint64_t* p_full = s_full + kPfQTiles;     // [2]  P of tile A / B written (softmax -> MMA)
-  uint64_t* pv_done = p_full + kPfQTiles;    // [2]  PV of tile A / B retired (MMA -> softmax)
-  uint64_t* o_empty = pv_done + kPfQTiles;   // [2]  O of tile A / B read out (softmax -> MMA)
+  uint64_t* s_full = empty + kSlots;         // [2] S of an even / odd tile ready (MMA -> softmax)
+  uint64_t* p_full = s_full + 2;             // [2] P of the tile written (softmax -> MMA)
+  uint64_t* pv_done = p_full + 2;            // [2] PV of the tile retired (MMA -> softmax)
+  uint64_t* m_ready = pv_done + 2;           // [2] running max after the tile published
+  uint64_t* o_full = m_ready + 2;            // [2] last PV of the item retired (MMA -> epilogue)
+  uint64_t* o_empty = o_full + 2;            // [2] O of the item read out (epilogue -> MMA)
+  uint64_t* stat_full = o_empty + 2;         // [2] both groups' (max, sum) written
+  uint64_t* stat_empty = stat_full + 2;      // [2] ... and read by the epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int group = warp >> 2;               // warpgroup = role
 
   // A CTA of this launch just gave up on a wait: do not repeat the timeout per CTA.
   if (timeout_drain_window(p.err_word)) return;
@@ -237,17 +255,21 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   };
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    for (int i = 0; i < kSlots; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
-    }
-    for (int i = 0; i < kPfQTiles; ++i) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
       mbar_init(&pv_done[i], 1);
+      mbar_init(&m_ready[i], 128);
+      mbar_init(&o_full[i], 1);
       mbar_init(&o_empty[i], 128);
+      mbar_init(&stat_full[i], 256);
+      mbar_init(&stat_empty[i], 128);
+    }
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -260,190 +282,222 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  // columns: S_A [0,128)  S_B [128,256)  O_A [256,256+HD)  O_B [384,384+HD)
+  // columns: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+HD)  O_1 [384,384+HD)
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_tensormap(&tm_q);
-      prefetch_tensormap(&tm_k);
-      prefetch_tensormap(&tm_v);
-    }
-    const uint64_t pol_q = l2_policy_evict_first();
-    const uint64_t pol_kv = l2_policy_evict_last();
-    uint32_t ring_i = 0, item_n = 0;
-    for (int round = 0; round < num_rounds; ++round) {
-      PrefillItem it;
-      if (!get_item(round, it)) continue;
-      const int kvh = it.head / p.group;
-      // Q may be overwritten once every QK of the previous item has retired.
-      mbar_wait(q_empty, (item_n & 1) ^ 1, abort_flag, p.err_word);
-      ++item_n;
+  if (group == 0) {
+    setmaxnreg_dec<kPfRegsProducer>();
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
       if (lane == 0) {
-        mbar_arrive_expect_tx(q_full, kPfQTiles * L::kTileBytes);
-#pragma unroll
-        for (int w = 0; w < kPfQTiles; ++w)
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+      }
+      const uint64_t pol_q = l2_policy_evict_first();
+      const uint64_t pol_kv = l2_policy_evict_last();
+      uint32_t ring_i = 0, item_n = 0;
+      for (int round = 0; round < num_rounds; ++round) {
+        PrefillItem it;
+        if (!get_item(round, it)) continue;
+        const int kvh = it.head / p.group;
+        const int ip = item_n & 1;
+        // the Q buffer is free once every QK of the item two back has retired
+        mbar_wait(&q_empty[ip], ((item_n >> 1) & 1) ^ 1, abort_flag, p.err_word);
+        ++item_n;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&q_full[ip], L::kTileBytes);
 #pragma unroll
           for (int s = 0; s < kSub; ++s)
-            tma_load_2d(q_smem + w * L::kTileBytes + s * L::kSubBytes, &tm_q, q_full,
-                        it.head * HD + s * 64, it.seq_q_begin + it.q0 + w * kPfM, pol_q);
-      }
-      const int32_t* pt = p.page_table + static_cast<int64_t>(it.seq) * p.page_table_stride;
-      const int last_pos = it.start + min(it.seq_len_q, it.q0 + kPfRowsPerItem) - 1;
-      const int n_pages = last_pos / BS + 1;      // pages holding keys 0 .. last_pos
-      for (int i = 0; i < 2 * it.n_max; ++i, ++ring_i) {
-        const int j = (WIN ? it.j0 : 0) + (i >> 1);          // absolute KV tile
-        const bool is_v = i & 1;
-        const int slot = ring_i % kSlots;
-        mbar_wait(&empty[slot], ((ring_i / kSlots) & 1) ^ 1, abort_flag, p.err_word);
-        uint8_t* dst = ring + slot * L::kTileBytes;
-        const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
-        if (lane == 0) mbar_arrive_expect_tx(&full[slot], L::kTileBytes);
-        if (p.kv_is_paged) {
-          int my_id = 0;
-          if (lane < kPagesPerTile) {
-            int idx = min(j * kPagesPerTile + lane, n_pages - 1);
-            idx = min(idx, p.page_table_width - 1);
-            my_id = pt[idx];
-          }
-#pragma unroll
-          for (int pg = 0; pg < kPagesPerTile; ++pg) {
-            int64_t blk = __shfl_sync(0xffffffffu, my_id, pg);
-            if (blk < 0 || blk >= p.num_blocks) {
-              if (lane == 0) atomicExch(p.err_word, kDevBadIndex);
-              blk = 0;
+            tma_load_2d(q_smem + ip * L::kTileBytes + s * L::kSubBytes, &tm_q, &q_full[ip],
+                        it.head * HD + s * 64, it.seq_q_begin + it.q0, pol_q);
+        }
+        const int32_t* pt = p.page_table + static_cast<int64_t>(it.seq) * p.page_table_stride;
+        const int last_pos = it.first_pos + it.rows_valid - 1;
+        const int n_pages = last_pos / BS + 1;      // pages holding keys 0 .. last_pos
+        for (int i = 0; i < 2 * it.n_tiles; ++i, ++ring_i) {
+          const int j = it.j0 + (i >> 1);                      // absolute KV tile
+          const bool is_v = i & 1;
+          const int slot = ring_i % kSlots;
+          mbar_wait(&empty[slot], ((ring_i / kSlots) & 1) ^ 1, abort_flag, p.err_word);
+          uint8_t* dst = ring + slot * L::kTileBytes;
+          const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+          if (lane == 0) mbar_arrive_expect_tx(&full[slot], L::kTileBytes);
+          if (p.kv_is_paged) {
+            int my_id = 0;
+            if (lane < kPagesPerTile) {
+              int idx = min(j * kPagesPerTile + lane, n_pages - 1);
+              idx = min(idx, p.page_table_width - 1);
+              my_id = pt[idx];
             }
-            if (lane == 0) {
-              const int32_t y = static_cast<int32_t>((blk * p.num_kv_heads + kvh) * BS);
 #pragma unroll
+            for (int pg = 0; pg < kPagesPerTile; ++pg) {
+              int64_t blk = __shfl_sync(0xffffffffu, my_id, pg);
+              if (blk < 0 || blk >= p.num_blocks) {
+                if (lane == 0) atomicExch(p.err_word, kDevBadIndex);
+                blk = 0;
+              }
+              if (lane == 0) {
+                const int32_t y = static_cast<int32_t>((blk * p.num_kv_heads + kvh) * BS);
+#pragma unroll
+                for (int s = 0; s < kSub; ++s)
+                  tma_load_2d(dst + s * L::kSubBytes + pg * BS * 128, tm, &full[slot], s * 64, y,
+                              pol_kv);
+              }
+            }
+          } else if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < kSub; ++s)
+              tma_load_2d(dst + s * L::kSubBytes, tm, &full[slot], kvh * HD + s * 64,
+                          it.seq_q_begin + j * kPfN, pol_kv);
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      // The whole warp walks the schedule (so addresses and descriptors stay warp-uniform);
+      // lane 0 issues.  Descriptor words are built once per tile: the k-step only adds a
+      // constant to the low word, so consecutive tcgen05.mma are a couple of instructions apart.
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfM, kPfN, false, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true);
+      // high descriptor word: SBO = 1024 B, descriptor version 1, 128-byte swizzle
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kLboV = (static_cast<uint32_t>(L::kSubBytes) >> 4) << 16;  // V: next 64 d
+      constexpr uint32_t kLboK = 1u << 16;                                          // unused field
+      const bool leader = lane == 0;
+      auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+      auto wait_ring = [&](uint32_t i) {
+        mbar_wait(&full[i % kSlots], (i / kSlots) & 1, abort_flag, p.err_word);
+        tc_fence_after_sync();
+      };
+      auto release_ring = [&](uint32_t i) {
+        if (leader) umma_commit(&empty[i % kSlots]);
+      };
+      // what this warp needs of an item: KV tile count, first KV tile, last query position
+      struct Slim {
+        int n_tiles, j0, last_pos;
+      };
+      auto next_item = [&](int& round, Slim& out) {
+        PrefillItem it;
+        for (; round < num_rounds; ++round) {
+          if (get_item(round, it)) {
+            out.n_tiles = it.n_tiles;
+            out.j0 = it.j0;
+            out.last_pos = it.first_pos + it.rows_valid - 1;
+            ++round;
+            return true;
+          }
+        }
+        return false;
+      };
+      // S_{t%2} = Q K_j^T of item number `item_no` (whose K_0 has ring index `ring_base`)
+      auto issue_qk = [&](const Slim& it, uint32_t item_no, uint32_t ring_base, int j,
+                          uint32_t t) {
+        const int ip = item_no & 1;
+        if (j == 0) {
+          mbar_wait(&q_full[ip], (item_no >> 1) & 1, abort_flag, p.err_word);
+          tc_fence_after_sync();
+        }
+        const uint32_t k_ring = ring_base + 2 * j;
+        wait_ring(k_ring);
+        const uint32_t q_lo = (smem_u32(q_smem + ip * L::kTileBytes) >> 4) | kLboK;
+        const uint32_t k_lo = (smem_u32(ring + (k_ring % kSlots) * L::kTileBytes) >> 4) | kLboK;
+        const uint32_t d = tmem_base + (t & 1u) * kPfN;
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = ((kk >> 2) * L::kSubBytes + (kk & 3) * 32) >> 4;
+            umma_ss(d, desc(q_lo + off), desc(k_lo + off), idesc_qk, kk > 0);
+          }
+          umma_commit(&s_full[t & 1u]);
+        }
+        release_ring(k_ring);
+        // the last QK of the item has been issued: its Q buffer is free once it retires
+        if (j == it.n_tiles - 1 && leader) umma_commit(&q_empty[ip]);
+      };
+
+      Slim cur, nxt;
+      int round = 0;
+      bool have_cur = next_item(round, cur), have_nxt = false;
+      uint32_t t = 0;              // KV tiles issued so far (all items)
+      uint32_t item_no = 0;        // items started so far
+      uint32_t ring_base = 0;      // ring index of K_0 of the current item
+      if (have_cur) issue_qk(cur, item_no, ring_base, 0, t);
+      while (have_cur) {
+        have_nxt = next_item(round, nxt);
+        const int ip = item_no & 1;
+        const int n = cur.n_tiles;
+        for (int j = 0; j < n; ++j, ++t) {
+          // one tile of look-ahead for the tensor pipe, across the item boundary too
+          if (j + 1 < n) {
+            issue_qk(cur, item_no, ring_base, j + 1, t + 1);
+          } else if (have_nxt) {
+            issue_qk(nxt, item_no + 1, ring_base + 2 * n, 0, t + 1);
+          }
+          const uint32_t v_ring = ring_base + 2 * j + 1;
+          wait_ring(v_ring);
+          if (j == n - 1) {
+            // Keys past the item's last query row are masked in P, but 0 x (stale, possibly
+            // non-finite cache contents) would still poison the row: zero those V rows.
+            const int first_dead = cur.last_pos + 1 - (cur.j0 + j) * kPfN;  // row inside the tile
+            if (first_dead < kPfN) {
+              uint8_t* vt = ring + (v_ring % kSlots) * L::kTileBytes;
+              const int vecs = (kPfN - first_dead) * 8;       // 16-byte vectors per 64-wide sub-tile
               for (int s = 0; s < kSub; ++s)
-                tma_load_2d(dst + s * L::kSubBytes + pg * BS * 128, tm, &full[slot], s * 64, y,
-                            pol_kv);
+                for (int i = lane; i < vecs; i += 32)
+                  *reinterpret_cast<uint4*>(vt + s * L::kSubBytes + first_dead * 128 + i * 16) =
+                      make_uint4(0u, 0u, 0u, 0u);
+              fence_proxy_async_smem();
+              __syncwarp();
             }
           }
-        } else if (lane == 0) {
+          mbar_wait(&p_full[t & 1u], (t >> 1) & 1, abort_flag, p.err_word);
+          if (j == 0)     // O of the item two back must have been read out before it is overwritten
+            mbar_wait(&o_empty[ip], ((item_no >> 1) & 1) ^ 1, abort_flag, p.err_word);
+          tc_fence_after_sync();
+          const uint32_t p_tmem = tmem_base + (t & 1u) * kPfN;   // P over the first 64 columns of S
+          const uint32_t v_lo = (smem_u32(ring + (v_ring % kSlots) * L::kTileBytes) >> 4) | kLboV;
+          const uint32_t d = tmem_base + 256 + ip * 128;
+          if (leader) {
 #pragma unroll
-          for (int s = 0; s < kSub; ++s)
-            tma_load_2d(dst + s * L::kSubBytes, tm, &full[slot], kvh * HD + s * 64,
-                        it.seq_q_begin + j * kPfN, pol_kv);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    // The whole warp walks the schedule (so addresses and descriptors stay warp-uniform);
-    // lane 0 issues.  Descriptor words are built once per tile: the k-step only adds a
-    // constant to the low word, so consecutive tcgen05.mma are a couple of instructions apart.
-    constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfM, kPfN, false, false);
-    constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true);
-    // high descriptor word: SBO = 1024 B, descriptor version 1, 128-byte swizzle
-    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    constexpr uint32_t kLboV = (static_cast<uint32_t>(L::kSubBytes) >> 4) << 16;  // V: next 64 d
-    constexpr uint32_t kLboK = 1u << 16;                                          // unused field
-    const bool leader = lane == 0;
-    auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
-    uint32_t ring_base = 0;            // ring index of K_0 of the current item
-    uint32_t item_n = 0;
-    uint32_t tiles_done[kPfQTiles] = {0, 0};   // KV tiles finished per query tile (all items)
-    uint32_t items_done[kPfQTiles] = {0, 0};   // items in which the query tile was active
-    auto wait_ring = [&](uint32_t i) {
-      mbar_wait(&full[i % kSlots], (i / kSlots) & 1, abort_flag, p.err_word);
-      tc_fence_after_sync();
-    };
-    auto release_ring = [&](uint32_t i) {
-      if (leader) umma_commit(&empty[i % kSlots]);
-    };
-    auto issue_qk = [&](int w, uint32_t k_ring) {   // S_w = Q_w K^T
-      const uint32_t q_lo = (smem_u32(q_smem + w * L::kTileBytes) >> 4) | kLboK;
-      const uint32_t k_lo = (smem_u32(ring + (k_ring % kSlots) * L::kTileBytes) >> 4) | kLboK;
-      const uint32_t d = tmem_base + w * kPfN;
-      if (leader) {
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * L::kSubBytes + (kk & 3) * 32) >> 4;
-          umma_ss(d, desc(q_lo + off), desc(k_lo + off), idesc_qk, kk > 0);
-        }
-        umma_commit(&s_full[w]);
-      }
-    };
-    auto issue_pv = [&](int w, bool first, uint32_t v_ring) {   // O_w (+)= P_w V_j
-      mbar_wait(&p_full[w], tiles_done[w] & 1, abort_flag, p.err_word);
-      if (first)    // O_w of the previous item must have been read out before it is overwritten
-        mbar_wait(&o_empty[w], (items_done[w] & 1) ^ 1, abort_flag, p.err_word);
-      tc_fence_after_sync();
-      const uint32_t p_tmem = tmem_base + w * kPfN;   // P over the first 64 columns of S_w
-      const uint32_t v_lo = (smem_u32(ring + (v_ring % kSlots) * L::kTileBytes) >> 4) | kLboV;
-      const uint32_t d = tmem_base + 256 + w * 128;
-      if (leader) {
-#pragma unroll
-        for (int kk = 0; kk < kPfN / 16; ++kk) {
-          // A: 16 keys = 8 packed 32-bit columns per step; B: 16 keys = 2048 B further on
-          umma_ts(d, p_tmem + kk * 8, desc(v_lo + kk * (2048 >> 4)), idesc_pv,
-                  !first || (kk > 0));
-        }
-        umma_commit(&pv_done[w]);
-      }
-      ++tiles_done[w];
-    };
-    for (int round = 0; round < num_rounds; ++round) {
-      PrefillItem it;
-      if (!get_item(round, it)) continue;
-      mbar_wait(q_full, item_n & 1, abort_flag, p.err_word);
-      ++item_n;
-      wait_ring(ring_base);                         // K_0
-#pragma unroll
-      for (int w = 0; w < kPfQTiles; ++w)
-        if (it.n_rel[w] > 0 && (!WIN || it.skip[w] == 0)) issue_qk(w, ring_base);
-      release_ring(ring_base);
-      if (it.n_max == 1 && leader) umma_commit(q_empty);
-      for (int j = 0; j < it.n_max; ++j) {
-        wait_ring(ring_base + 2 * j + 1);           // V_j
-        const bool has_next = j + 1 < it.n_max;
-        bool next_k_ready = false;
-#pragma unroll
-        for (int w = 0; w < kPfQTiles; ++w) {
-          const int skip_w = WIN ? it.skip[w] : 0;
-          if (j >= skip_w && j < it.n_rel[w]) issue_pv(w, j == skip_w, ring_base + 2 * j + 1);
-          if (j + 1 >= skip_w && j + 1 < it.n_rel[w]) {
-            if (!next_k_ready) {
-              wait_ring(ring_base + 2 * j + 2);   // K_{j+1}
-              next_k_ready = true;
+            for (int kk = 0; kk < kPfN / 16; ++kk) {
+              // A: 16 keys = 8 packed 32-bit columns per step; B: 16 keys = 2048 B further on
+              umma_ts(d, p_tmem + kk * 8, desc(v_lo + kk * (2048 >> 4)), idesc_pv,
+                      (j > 0) || (kk > 0));
             }
-            issue_qk(w, ring_base + 2 * j + 2);
+            umma_commit(&pv_done[t & 1u]);
+            if (j == n - 1) umma_commit(&o_full[ip]);
           }
+          release_ring(v_ring);
         }
-        release_ring(ring_base + 2 * j + 1);
-        if (has_next) {
-          release_ring(ring_base + 2 * j + 2);
-          // the last QK of the item has been issued: Q is free once it retires
-          if (j + 2 == it.n_max && leader) umma_commit(q_empty);
-        }
+        ring_base += 2 * n;
+        ++item_no;
+        cur = nxt;
+        have_cur = have_nxt;
       }
-#pragma unroll
-      for (int w = 0; w < kPfQTiles; ++w)
-        if (it.n_rel[w] > 0) ++items_done[w];
-      ring_base += 2 * it.n_max;
     }
-  } else {
-    // ------------------------------------------------------------------ softmax / epilogue
-    const int w = (warp - 2) >> 2;                       // 0 = tile A, 1 = tile B
+  } else if (group <= 2) {
+    // ------------------------------------------------------------------ softmax, even / odd tiles
+    setmaxnreg_inc<kPfRegsSoftmax>();
+    const uint32_t w = group - 1;                        // parity of the tiles this group takes
     const int row = (warp & 3) * 32 + lane;              // tensor-memory lane == query row
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_addr = tmem_base + w * kPfN + lane_addr;
-    const uint32_t o_addr = tmem_base + 256 + w * 128 + lane_addr;
     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-    uint32_t tiles_done = 0;            // KV tiles this warpgroup has finished (all items)
+    uint32_t t0 = 0;                    // global index of the item's first tile
+    uint32_t item_no = 0;
     for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
       if (!get_item(round, it)) continue;
-      if (it.n_rel[w] <= 0) continue;
-      const int q_pos = it.first_pos[w] + row;
-      float m_run = -INFINITY, l_run = 0.f;
-      const int skip_w = WIN ? it.skip[w] : 0;
-      for (int jr = skip_w; jr < it.n_rel[w]; ++jr, ++tiles_done) {
-        const int j = (WIN ? it.j0 : 0) + jr;    // absolute KV tile
-        const bool first = jr == skip_w;
-        mbar_wait(&s_full[w], tiles_done & 1, abort_flag, p.err_word);
+      const int ip = item_no & 1;
+      const uint32_t o_addr = tmem_base + 256 + ip * 128 + lane_addr;
+      const int q_pos = it.first_pos + row;
+      float l_run = 0.f, m_last = -INFINITY;   // this group's row sum, relative to m_last
+      for (int jr = 0; jr < it.n_tiles; ++jr) {
+        const uint32_t t = t0 + jr;
+        if ((t & 1u) != w) continue;
+        const uint32_t k = t >> 1;                       // how many tiles of this parity came before
+        const int j = it.j0 + jr;                        // absolute KV tile
+        mbar_wait(&s_full[w], k & 1, abort_flag, p.err_word);
         tc_fence_after_sync();
         uint32_t sreg[4][32];
 #pragma unroll
@@ -451,19 +505,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         tmem_wait_ld();
 
         const int key0 = j * kPfN;
-        if (key0 + kPfN - 1 > it.first_pos[w]) {   // tile crosses the diagonal for some row
+        if (key0 + kPfN - 1 > it.first_pos) {   // tile crosses the diagonal for some row
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
-              if (key0 + c * 32 + k > q_pos) sreg[c][k] = 0xff800000u;   // -inf
+            for (int kx = 0; kx < 32; ++kx)
+              if (key0 + c * 32 + kx > q_pos) sreg[c][kx] = 0xff800000u;   // -inf
         }
-        if (WIN && key0 < it.first_pos[w] + kPfM - p.window) {   // below some row's window
+        if (WIN && key0 < it.first_pos + kPfM - p.window) {   // below some row's window
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
-              if (key0 + c * 32 + k + p.window <= q_pos) sreg[c][k] = 0xff800000u;   // -inf
+            for (int kx = 0; kx < 32; ++kx)
+              if (key0 + c * 32 + kx + p.window <= q_pos) sreg[c][kx] = 0xff800000u;   // -inf
         }
         // row max of the raw scores (scale > 0), four independent chains
         float mx[4];
@@ -472,21 +526,29 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           mx[c] = max3(__uint_as_float(sreg[c][0]), __uint_as_float(sreg[c][1]),
                        __uint_as_float(sreg[c][2]));
 #pragma unroll
-          for (int k = 3; k + 1 < 32; k += 2)
-            mx[c] = max3(mx[c], __uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1]));
+          for (int kx = 3; kx + 1 < 32; kx += 2)
+            mx[c] = max3(mx[c], __uint_as_float(sreg[c][kx]), __uint_as_float(sreg[c][kx + 1]));
           mx[c] = fmaxf(mx[c], __uint_as_float(sreg[c][31]));
         }
         const float mx_s = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
-        float m_new = m_run;
-        if (mx_s - m_run > kPfRescaleThreshold) m_new = mx_s;   // also taken when m_run = -inf
+        // running max after the tile before (the other group publishes it as soon as it has it)
+        float m_prev = -INFINITY;
+        if (t > 0) {
+          const uint32_t other = (t + 1) >> 1;           // tiles of the other parity before t
+          mbar_wait(&m_ready[w ^ 1u], (other - 1) & 1, abort_flag, p.err_word);
+          if (jr > 0) m_prev = m_sh[(w ^ 1u) * kPfM + row];
+        }
+        float m_new = m_prev;
+        if (mx_s - m_prev > kPfRescaleThreshold) m_new = mx_s;   // also taken when m_prev = -inf
+        m_sh[w * kPfM + row] = m_new;
+        mbar_arrive(&m_ready[w]);
         // a row whose keys are all masked so far (possible only under a sliding window) keeps
         // m = -inf: its weights and its correction factor are 0, not exp2(-inf + inf)
-        const float corr = (WIN && m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
-        const bool rescale = (m_new != m_run) && !first;
-        m_run = m_new;
+        const bool rescale = (jr > 0) && (m_new != m_prev);
         // p = 2^(s*scale - m): packed FMA, then ex2; two packed running sums.  Each 32-key
-        // chunk goes straight back to tensor memory as 16 packed bf16x2 columns.  QK_j has
-        // retired (s_full), and PV_{j-1} was issued before it, so S_w / P_w / O_w are quiescent.
+        // chunk goes straight back to tensor memory as 16 packed bf16x2 columns.  QK of this
+        // tile has retired (s_full) and the PV that read the buffer before was issued ahead of
+        // it, so the S / P columns are quiescent.
         const float m_sub = (WIN && m_new == -INFINITY) ? 0.f : m_new;
         const uint64_t negm2 = pack_f32x2(-m_sub, -m_sub);
         uint64_t sum2[2] = {0ull, 0ull};
@@ -494,15 +556,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int c = 0; c < 4; ++c) {
           uint32_t preg[16];
 #pragma unroll
-          for (int k = 0; k < 32; k += 2) {
+          for (int kx = 0; kx < 32; kx += 2) {
             const uint64_t x2 = fma_f32x2(
-                pack_f32x2(__uint_as_float(sreg[c][k]), __uint_as_float(sreg[c][k + 1])), scale2,
+                pack_f32x2(__uint_as_float(sreg[c][kx]), __uint_as_float(sreg[c][kx + 1])), scale2,
                 negm2);
             float x0, x1;
             unpack_f32x2(x2, x0, x1);
             const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-            sum2[(k >> 1) & 1] = add_f32x2(sum2[(k >> 1) & 1], pack_f32x2(e0, e1));
-            preg[k >> 1] = pack_bf16x2(e0, e1);
+            sum2[(kx >> 1) & 1] = add_f32x2(sum2[(kx >> 1) & 1], pack_f32x2(e0, e1));
+            preg[kx >> 1] = pack_bf16x2(e0, e1);
           }
           tmem_st_32x16(s_addr + c * 16, preg);
         }
@@ -510,24 +572,32 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           float a0, a1, b0, b1;
           unpack_f32x2(sum2[0], a0, a1);
           unpack_f32x2(sum2[1], b0, b1);
-          l_run = l_run * corr + ((a0 + a1) + (b0 + b1));
+          // this group's sum is relative to the max at ITS previous tile
+          const float f = (m_last == -INFINITY) ? 0.f : fast_exp2(m_last - m_new);
+          l_run = l_run * f + ((a0 + a1) + (b0 + b1));
+          m_last = m_new;
         }
-        // O row rescale (rare: only when the running max moved by more than the threshold).
-        if (!first && __any_sync(0xffffffffu, rescale)) {
-          const float f = rescale ? corr : 1.f;
-          const uint64_t f2 = pack_f32x2(f, f);
+        // O row rescale (rare: only when the running max moved by more than the threshold):
+        // every PV up to the tile before must have retired; PV of this tile waits for p_full.
+        if (__any_sync(0xffffffffu, rescale)) {
+          const uint32_t other = (t + 1) >> 1;
+          mbar_wait(&pv_done[w ^ 1u], (other - 1) & 1, abort_flag, p.err_word);
+          tc_fence_after_sync();
+          const float corr =
+              !rescale ? 1.f : ((WIN && m_prev == -INFINITY) ? 0.f : fast_exp2(m_prev - m_new));
+          const uint64_t f2 = pack_f32x2(corr, corr);
 #pragma unroll
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t oreg[32];
             tmem_ld_32x32(o_addr + c * 32, oreg);
             tmem_wait_ld();
 #pragma unroll
-            for (int k = 0; k < 32; k += 2) {
+            for (int kx = 0; kx < 32; kx += 2) {
               float y0, y1;
-              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(oreg[k]),
-                                                __uint_as_float(oreg[k + 1])), f2), y0, y1);
-              oreg[k] = __float_as_uint(y0);
-              oreg[k + 1] = __float_as_uint(y1);
+              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(oreg[kx]),
+                                                __uint_as_float(oreg[kx + 1])), f2), y0, y1);
+              oreg[kx] = __float_as_uint(y0);
+              oreg[kx + 1] = __float_as_uint(y1);
             }
             tmem_st_32x32(o_addr + c * 32, oreg);
           }
@@ -536,33 +606,62 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_fence_before_sync();
         mbar_arrive(&p_full[w]);
       }
-      // ---- item epilogue: O / l -> bf16 rows.  O_w is handed back to the MMA warp as soon as
-      // it sits in registers, so PV_0 of the next item does not wait for the global stores.
-      mbar_wait(&pv_done[w], (tiles_done - 1) & 1, abort_flag, p.err_word);
+      // ---- item end: hand this group's (max, sum) of the row to the epilogue
+      mbar_wait(&stat_empty[ip], ((item_no >> 1) & 1) ^ 1, abort_flag, p.err_word);
+      stat_sh[(ip * 2 + w) * kPfM + row] = make_float2(m_last, l_run);
+      mbar_arrive(&stat_full[ip]);
+      t0 += it.n_tiles;
+      ++item_no;
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    setmaxnreg_dec<kPfRegsEpilogue>();
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t item_no = 0;
+    for (int round = 0; round < num_rounds; ++round) {
+      PrefillItem it;
+      if (!get_item(round, it)) continue;
+      const int ip = item_no & 1;
+      const uint32_t ph = (item_no >> 1) & 1;
+      const uint32_t o_addr = tmem_base + 256 + ip * 128 + lane_addr;
+      mbar_wait(&stat_full[ip], ph, abort_flag, p.err_word);
+      const float2 s0 = stat_sh[(ip * 2 + 0) * kPfM + row];
+      const float2 s1 = stat_sh[(ip * 2 + 1) * kPfM + row];
+      mbar_arrive(&stat_empty[ip]);
+      // O is relative to the max after the last tile, which is the larger of the two
+      const float m_fin = fmaxf(s0.x, s1.x);
+      const float l = (s0.x == -INFINITY ? 0.f : s0.y * fast_exp2(s0.x - m_fin)) +
+                      (s1.x == -INFINITY ? 0.f : s1.y * fast_exp2(s1.x - m_fin));
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      mbar_wait(&o_full[ip], ph, abort_flag, p.err_word);
       tc_fence_after_sync();
-      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint32_t oreg[HD / 32][32];
+      __nv_bfloat16* orow =
+          p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + row) * p.out_row_stride +
+          static_cast<int64_t>(it.head) * HD;
+      const bool store = row < it.rows_valid;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) tmem_ld_32x32(o_addr + c * 32, oreg[c]);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(&o_empty[w]);
-      uint32_t packed[HD / 2];
+      for (int c = 0; c < HD / 16; ++c) {
+        uint32_t oreg[16];
+        tmem_ld_32x16(o_addr + c * 16, oreg);
+        tmem_wait_ld();
+        if (c == HD / 16 - 1) {      // O sits in registers: hand the buffer back to the MMA warp
+          tc_fence_before_sync();
+          mbar_arrive(&o_empty[ip]);
+        }
+        uint32_t packed[8];
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c)
-#pragma unroll
-        for (int k = 0; k < 32; k += 2)
-          packed[(c * 32 + k) >> 1] = pack_bf16x2(__uint_as_float(oreg[c][k]) * inv_l,
-                                                  __uint_as_float(oreg[c][k + 1]) * inv_l);
-      if (row < it.rows_valid[w]) {
-        __nv_bfloat16* orow =
-            p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + w * kPfM + row) * p.out_row_stride +
-            static_cast<int64_t>(it.head) * HD;
-#pragma unroll
-        for (int k = 0; k < HD / 2; k += 4)
-          *reinterpret_cast<uint4*>(orow + 2 * k) =
-              make_uint4(packed[k], packed[k + 1], packed[k + 2], packed[k + 3]);
+        for (int kx = 0; kx < 16; kx += 2)
+          packed[kx >> 1] = pack_bf16x2(__uint_as_float(oreg[kx]) * inv_l,
+                                        __uint_as_float(oreg[kx + 1]) * inv_l);
+        if (store) {
+          *reinterpret_cast<uint4*>(orow + c * 16) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
+              make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
       }
+      ++item_no;
     }
   }
 
