@@ -29,6 +29,9 @@ __device__ __align__(16) int g_err_word[4] = {0, 0, 0, 0};
 static __device__ __align__(256) unsigned char g_static_workspace[B200ATTN_STATIC_WORKSPACE_BYTES];
 
 constexpr int kMaxDevices = 64;
+#ifdef B200ATTN_PF_TRACE
+static unsigned long long* g_pf_trace = nullptr;
+#endif
 
 struct DeviceInfo {
   bool ready = false;
@@ -772,12 +775,20 @@ int b200attn_prefill_ex(void* out, int64_t out_row_stride, const void* q, int64_
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err_word = dev->err_word;
+#ifdef B200ATTN_PF_TRACE
+  p.trace = g_pf_trace;
+#endif
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (head_size == 128 && block_size == 64) return launch_prefill<128, 64>(tq, tk, tv, p, dev->sm_count, s);
   if (head_size == 128) return launch_prefill<128, 32>(tq, tk, tv, p, dev->sm_count, s);
   if (block_size == 64) return launch_prefill<64, 64>(tq, tk, tv, p, dev->sm_count, s);
   return launch_prefill<64, 32>(tq, tk, tv, p, dev->sm_count, s);
 }
+
+#ifdef B200ATTN_PF_TRACE
+// Debug builds only: device buffer [CTAs][6][8] of cycle counters the prefill kernel fills.
+void b200attn_debug_set_prefill_trace(unsigned long long* dev_buffer) { g_pf_trace = dev_buffer; }
+#endif
 
 int b200attn_paged_decode_static(void* out, int64_t out_row_stride, const void* q,
                                  int64_t q_row_stride, const void* k_cache, const void* v_cache,

@@ -2,18 +2,24 @@
 //
 // Persistent kernel: one CTA per SM walks a list of work items; an item is 128 query rows of
 // one sequence x one query head.  KV is consumed in tiles of 128 keys.  Four warpgroups:
-//   warpgroup 0   warp 0: TMA producer: per item the Q tile (two Q buffers, so the next item's
-//                 Q lands while this one is still in use), then K_0, V_0, K_1, V_1, ... into a
-//                 ring of swizzled [128 rows x 128 B] sub-tiles (paged source: one box per page;
-//                 fresh source: one box per 64-wide column group).
-//                 warp 1: allocates tensor memory once (S_0, S_1, O_0, O_1 = 512 columns) and
-//                 issues tcgen05.mma from one lane.  S is double-buffered by KV tile, so
-//                 QK(t+1) is issued BEFORE the softmax of tile t has produced P(t):
-//                     QK(t+1), [wait P(t)] PV(t), QK(t+2), [wait P(t+1)] PV(t+1), ...
-//                 the tile counter t runs on across items, so the first QK of the next item is
-//                 in flight while the last tiles of this one are still in their softmax.
-//                 O is double-buffered by item, so the next item accumulates while the epilogue
-//                 warpgroup reads this one out.
+//   warpgroup 0   warps 0 and 2: TMA producers.  Warp 0 loads, per item, the Q tile (two Q
+//                 buffers, so the next item's Q lands while this one is still in use) and the K
+//                 tiles; warp 2 loads the V tiles.  K and V have rings of their own (swizzled
+//                 [128 rows x 128 B] sub-tiles; paged source: one box per page; fresh source:
+//                 one box per 64-wide column group): QK runs ahead of PV, so a K tile must not
+//                 queue behind the V tiles that are still waiting for their P.
+//                 warps 1 and 3: tcgen05.mma issuers, one lane each.  Warp 1 (which also owns the
+//                 tensor-memory allocation: S_0, S_1, S_2, O = 512 columns) issues S_{t%3} =
+//                 Q K_t^T as soon as K_t has landed and the PV that read the buffer three tiles
+//                 ago has retired; warp 3 issues O (+)= P_t V_t as soon as the softmax has
+//                 written P_t.  Two issuers because the tensor pipe's queue is short: a single
+//                 thread that also waits on four barriers per tile leaves the pipe idle half of
+//                 the time (measured).  The tile counter t runs on across items, so the QKs of
+//                 the next item are in flight while the last tiles of this one are still in
+//                 their softmax; only the first PV of an item waits for the epilogue to have
+//                 read the item before out of O.  One tcgen05.commit per MMA group: the barrier
+//                 that tells the softmax "S is ready" is the same one that tells the K producer
+//                 "the slot is free", and likewise for PV / the V producer / the epilogue.
 //   warpgroups 1, 2   softmax of the even / odd tiles, one thread per query row: tcgen05.ld the
 //                 row of S, causal mask on the diagonal tile, row max; the running max of a row
 //                 is handed from tile to tile through shared memory (the only serial link
@@ -24,7 +30,7 @@
 //                 operand from tensor memory); rescales the O row in tensor memory in the rare
 //                 case that the running max moved by more than a threshold.
 //   warpgroup 3   epilogue: per item, waits for the last PV, merges the two warpgroups' row
-//                 sums, normalises O by 1/l and stores bf16 rows; hands O back at once.
+//                 sums, reads O, hands it back, normalises by 1/l and stores bf16 rows.
 // Registers follow the roles (setmaxnreg): the two softmax warpgroups hold a whole S row each.
 // Items are ordered heaviest first (by the index of the 128-row block inside its sequence,
 // highest first, heads of one block adjacent) and dealt to the CTAs in rounds of alternating
@@ -40,6 +46,16 @@ constexpr int kPfRowsPerItem = kPfM;
 constexpr int kPfN = 128;        // keys per KV tile
 constexpr int kPfThreads = 512;  // four warpgroups
 constexpr float kPfRescaleThreshold = 8.f;  // log2 units
+// One pair of exponentials in every kPfPolyEvery is computed on the FMA pipe (a cubic on the
+// fractional part, the integer part added to the exponent field) instead of the MUFU: the
+// special-function unit is the busiest pipe of the softmax warps, the FMA pipe the idlest.
+// Relative error of the cubic 1.0e-4, far below the bf16 rounding of P.  0 = MUFU only, which is
+// the default: on config 2 every fourth pair measured 834 TFLOP/s, every second 779, none 918
+// (the softmax warps are short of issue slots, not of MUFU throughput).
+#ifndef B200ATTN_PF_POLY_EVERY
+#define B200ATTN_PF_POLY_EVERY 0
+#endif
+constexpr int kPfPolyEvery = B200ATTN_PF_POLY_EVERY;
 constexpr int kPfSeqCache = 1024;           // sequences whose cu_q is cached in shared memory
 constexpr int kPfLevelOrderMaxSeqs = 64;    // above this, items keep plain sequence order
 constexpr int kPfItemTable = 128;           // rounds whose item is decoded once, up front
@@ -66,14 +82,37 @@ struct PrefillParams {
   int64_t num_blocks;
   float scale_log2;
   int* err_word;
+#ifdef B200ATTN_PF_TRACE
+  unsigned long long* trace;   // [CTA][role 0..5][8] cycles spent per wait site (debug builds only)
+#endif
 };
+
+// Debug builds (-DB200ATTN_PF_TRACE) time every wait site with clock64; product builds compile
+// the macros away.
+#ifdef B200ATTN_PF_TRACE
+#define PF_TRACE_DECL unsigned long long tr_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tr_t0 = 0;
+#define PF_TRACE_BEGIN() tr_t0 = clock64()
+#define PF_TRACE_END(site) tr_acc[site] += clock64() - tr_t0
+#define PF_TRACE_FLUSH(role)                                                        \
+  if (lane == 0 && p.trace)                                                          \
+    for (int i_ = 0; i_ < 8; ++i_)                                                   \
+      p.trace[(static_cast<size_t>(blockIdx.x) * 6 + (role)) * 8 + i_] = tr_acc[i_];
+#else
+#define PF_TRACE_DECL
+#define PF_TRACE_BEGIN()
+#define PF_TRACE_END(site)
+#define PF_TRACE_FLUSH(role)
+#endif
 
 template <int HD>
 struct PrefillSmem {
   static constexpr int kSub = HD / 64;
   static constexpr int kSubBytes = 128 * 128;             // 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;     // one Q, K or V tile
-  static constexpr int kSlots = (HD == 128) ? 4 : 8;      // ring slots (one K or V tile each)
+  // K ring and V ring.  At most 3 tiles per ring: a producer learns that slot t % kRing is free
+  // from the S / PV barrier of tile t - kRing, which is shared with tile t - kRing + 3.
+  static constexpr int kRing = (HD == 128) ? 2 : 3;       // tiles per ring
+  static constexpr int kSlots = 2 * kRing;
   static constexpr int kQOff = 0;                         // two Q buffers (by item parity)
   static constexpr int kRingOff = 2 * kTileBytes;
   static constexpr int kSeqOff = kRingOff + kSlots * kTileBytes;
@@ -81,9 +120,9 @@ struct PrefillSmem {
   static constexpr int kMaxOff = kItemOff + kPfItemTable * 16;       // running max [tile parity][row]
   static constexpr int kStatOff = kMaxOff + 2 * kPfM * 4;            // (max, sum) [item parity][group][row]
   static constexpr int kBarOff = kStatOff + 2 * 2 * kPfM * 8;
-  // q_full[2] q_empty[2] full[kSlots] empty[kSlots] s_full[2] p_full[2] pv_done[2] m_ready[2]
-  // o_full[2] o_empty[2] stat_full[2] stat_empty[2]
-  static constexpr int kNumBars = 4 + 2 * kSlots + 16;
+  // q_full[2] q_empty[2] k_full[kRing] v_full[kRing] k_empty[kRing] v_empty[kRing] s_full[3] p_full[3] pv_done[3] m_ready[2]
+  // o_full o_empty stat_full[2] stat_empty[2]
+  static constexpr int kNumBars = 4 + 2 * kSlots + 17;
   static constexpr int kTotalBytes = kBarOff + kNumBars * 8 + 16 + 1024;
   static_assert(kItemOff % 16 == 0, "16-byte vector access alignment");
   static_assert(kBarOff % 8 == 0, "barrier alignment");
@@ -219,15 +258,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* q_full = bars;                   // [2] Q of the item landed (TMA -> MMA)
   uint64_t* q_empty = bars + 2;              // [2] last QK of the item retired (MMA -> TMA)
-  uint64_t* full = bars + 4;                 // [kSlots]
-  uint64_t* empty = full + kSlots;           // [kSlots]
-  uint64_t* s_full = empty + kSlots;         // [2] S of an even / odd tile ready (MMA -> softmax)
-  uint64_t* p_full = s_full + 2;             // [2] P of the tile written (softmax -> MMA)
-  uint64_t* pv_done = p_full + 2;            // [2] PV of the tile retired (MMA -> softmax)
-  uint64_t* m_ready = pv_done + 2;           // [2] running max after the tile published
-  uint64_t* o_full = m_ready + 2;            // [2] last PV of the item retired (MMA -> epilogue)
-  uint64_t* o_empty = o_full + 2;            // [2] O of the item read out (epilogue -> MMA)
-  uint64_t* stat_full = o_empty + 2;         // [2] both groups' (max, sum) written
+  constexpr int kRing = L::kRing;
+  uint64_t* k_full = bars + 4;               // [kRing] K tile landed (TMA -> MMA)
+  uint64_t* v_full = k_full + kRing;         // [kRing]
+  // S of tile t in buffer t%3 ready = QK(t) retired: wakes the softmax, and tells the K producer
+  // that the K slot is free again
+  uint64_t* s_full = v_full + kRing;         // [3]
+  uint64_t* p_full = s_full + 3;             // [3] P of the tile written (softmax -> PV issuer)
+  // PV(t) retired: S_{t%3} may be overwritten (QK issuer), the V slot is free (V producer), O may
+  // be rescaled (softmax), and after an item's last tile O is complete (epilogue)
+  uint64_t* pv_done = p_full + 3;            // [3]
+  uint64_t* m_ready = pv_done + 3;           // [2] running max after an even / odd tile published
+  uint64_t* o_empty = m_ready + 2;           // O of the item read out (epilogue -> PV issuer)
+  uint64_t* stat_full = o_empty + 1;         // [2] both groups' (max, sum) written
   uint64_t* stat_empty = stat_full + 2;      // [2] ... and read by the epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -258,18 +301,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
-      mbar_init(&pv_done[i], 1);
       mbar_init(&m_ready[i], 128);
-      mbar_init(&o_full[i], 1);
-      mbar_init(&o_empty[i], 128);
       mbar_init(&stat_full[i], 256);
       mbar_init(&stat_empty[i], 128);
     }
-    for (int i = 0; i < kSlots; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&pv_done[i], 1);
+    }
+    mbar_init(o_empty, 128);
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -282,45 +326,62 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  // columns: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+HD)  O_1 [384,384+HD)
+  // columns: S_0 [0,128)  S_1 [128,256)  S_2 [256,384)  O [384,384+HD)
 
   if (group == 0) {
     setmaxnreg_dec<kPfRegsProducer>();
-    if (warp == 0) {
-      // ------------------------------------------------------------------ TMA producer
+    if (warp == 0 || warp == 2) {
+      // ------------------------------------------------------------------ TMA producers
+      // warp 0: Q and K tiles; warp 2: V tiles.  Ring slot of tile t (counted over all items of
+      // this CTA): t % kRing of the K ring / of the V ring.
+      const bool is_v = warp == 2;
       if (lane == 0) {
-        prefetch_tensormap(&tm_q);
-        prefetch_tensormap(&tm_k);
-        prefetch_tensormap(&tm_v);
+        prefetch_tensormap(is_v ? &tm_v : &tm_k);
+        if (!is_v) prefetch_tensormap(&tm_q);
       }
       const uint64_t pol_q = l2_policy_evict_first();
       const uint64_t pol_kv = l2_policy_evict_last();
-      uint32_t ring_i = 0, item_n = 0;
+      const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+      uint64_t* full = is_v ? v_full : k_full;
+      uint64_t* retired = is_v ? pv_done : s_full;    // the MMA group that read a slot has retired
+      uint8_t* my_ring = ring + (is_v ? kRing * L::kTileBytes : 0);
+      uint32_t t = 0, item_n = 0;
+      PF_TRACE_DECL
+#ifdef B200ATTN_PF_TRACE
+      const long long tr_start = clock64();
+#endif
       for (int round = 0; round < num_rounds; ++round) {
         PrefillItem it;
         if (!get_item(round, it)) continue;
         const int kvh = it.head / p.group;
-        const int ip = item_n & 1;
-        // the Q buffer is free once every QK of the item two back has retired
-        mbar_wait(&q_empty[ip], ((item_n >> 1) & 1) ^ 1, abort_flag, p.err_word);
-        ++item_n;
-        if (lane == 0) {
-          mbar_arrive_expect_tx(&q_full[ip], L::kTileBytes);
+        if (!is_v) {
+          const int ip = item_n & 1;
+          // the Q buffer is free once every QK of the item two back has retired
+          PF_TRACE_BEGIN();
+          mbar_wait(&q_empty[ip], ((item_n >> 1) & 1) ^ 1, abort_flag, p.err_word);
+          PF_TRACE_END(0);
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&q_full[ip], L::kTileBytes);
 #pragma unroll
-          for (int s = 0; s < kSub; ++s)
-            tma_load_2d(q_smem + ip * L::kTileBytes + s * L::kSubBytes, &tm_q, &q_full[ip],
-                        it.head * HD + s * 64, it.seq_q_begin + it.q0, pol_q);
+            for (int s = 0; s < kSub; ++s)
+              tma_load_2d(q_smem + ip * L::kTileBytes + s * L::kSubBytes, &tm_q, &q_full[ip],
+                          it.head * HD + s * 64, it.seq_q_begin + it.q0, pol_q);
+          }
         }
+        ++item_n;
         const int32_t* pt = p.page_table + static_cast<int64_t>(it.seq) * p.page_table_stride;
         const int last_pos = it.first_pos + it.rows_valid - 1;
         const int n_pages = last_pos / BS + 1;      // pages holding keys 0 .. last_pos
-        for (int i = 0; i < 2 * it.n_tiles; ++i, ++ring_i) {
-          const int j = it.j0 + (i >> 1);                      // absolute KV tile
-          const bool is_v = i & 1;
-          const int slot = ring_i % kSlots;
-          mbar_wait(&empty[slot], ((ring_i / kSlots) & 1) ^ 1, abort_flag, p.err_word);
-          uint8_t* dst = ring + slot * L::kTileBytes;
-          const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+        for (int i = 0; i < it.n_tiles; ++i, ++t) {
+          const int j = it.j0 + i;                             // absolute KV tile
+          const int slot = t % kRing;
+          if (t >= static_cast<uint32_t>(kRing)) {     // the slot held tile t - kRing
+            const uint32_t u = t - kRing;
+            PF_TRACE_BEGIN();
+            mbar_wait(&retired[u % 3u], (u / 3u) & 1, abort_flag, p.err_word);
+            PF_TRACE_END(1);
+          }
+          uint8_t* dst = my_ring + slot * L::kTileBytes;
           if (lane == 0) mbar_arrive_expect_tx(&full[slot], L::kTileBytes);
           if (p.kv_is_paged) {
             int my_id = 0;
@@ -352,11 +413,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
         }
       }
-    } else if (warp == 1) {
-      // ------------------------------------------------------------------ MMA issuer
-      // The whole warp walks the schedule (so addresses and descriptors stay warp-uniform);
-      // lane 0 issues.  Descriptor words are built once per tile: the k-step only adds a
-      // constant to the low word, so consecutive tcgen05.mma are a couple of instructions apart.
+#ifdef B200ATTN_PF_TRACE
+      tr_acc[7] = clock64() - tr_start;
+      tr_acc[6] = t;
+#endif
+      PF_TRACE_FLUSH(is_v ? 1 : 0)
+    } else {
+      // ------------------------------------------------------------------ MMA issuers
+      // warp 1: QK, warp 3: PV.  The whole warp walks the schedule (so addresses and descriptors
+      // stay warp-uniform); lane 0 issues.
+      const bool is_pv = warp == 3;
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfM, kPfN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true);
       // high descriptor word: SBO = 1024 B, descriptor version 1, 128-byte swizzle
@@ -364,116 +430,102 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       constexpr uint32_t kLboV = (static_cast<uint32_t>(L::kSubBytes) >> 4) << 16;  // V: next 64 d
       constexpr uint32_t kLboK = 1u << 16;                                          // unused field
       const bool leader = lane == 0;
+      PF_TRACE_DECL
+#ifdef B200ATTN_PF_TRACE
+      const long long tr_start = clock64();
+#endif
       auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
-      auto wait_ring = [&](uint32_t i) {
-        mbar_wait(&full[i % kSlots], (i / kSlots) & 1, abort_flag, p.err_word);
-        tc_fence_after_sync();
-      };
-      auto release_ring = [&](uint32_t i) {
-        if (leader) umma_commit(&empty[i % kSlots]);
-      };
-      // what this warp needs of an item: KV tile count, first KV tile, last query position
-      struct Slim {
-        int n_tiles, j0, last_pos;
-      };
-      auto next_item = [&](int& round, Slim& out) {
+      uint8_t* k_ring = ring;
+      uint8_t* v_ring = ring + kRing * L::kTileBytes;
+      uint32_t t = 0, item_no = 0;
+      for (int round = 0; round < num_rounds; ++round) {
         PrefillItem it;
-        for (; round < num_rounds; ++round) {
-          if (get_item(round, it)) {
-            out.n_tiles = it.n_tiles;
-            out.j0 = it.j0;
-            out.last_pos = it.first_pos + it.rows_valid - 1;
-            ++round;
-            return true;
-          }
-        }
-        return false;
-      };
-      // S_{t%2} = Q K_j^T of item number `item_no` (whose K_0 has ring index `ring_base`)
-      auto issue_qk = [&](const Slim& it, uint32_t item_no, uint32_t ring_base, int j,
-                          uint32_t t) {
+        if (!get_item(round, it)) continue;
+        const int n = it.n_tiles;
         const int ip = item_no & 1;
-        if (j == 0) {
+        if (!is_pv) {
+          PF_TRACE_BEGIN();
           mbar_wait(&q_full[ip], (item_no >> 1) & 1, abort_flag, p.err_word);
-          tc_fence_after_sync();
+          PF_TRACE_END(0);
         }
-        const uint32_t k_ring = ring_base + 2 * j;
-        wait_ring(k_ring);
         const uint32_t q_lo = (smem_u32(q_smem + ip * L::kTileBytes) >> 4) | kLboK;
-        const uint32_t k_lo = (smem_u32(ring + (k_ring % kSlots) * L::kTileBytes) >> 4) | kLboK;
-        const uint32_t d = tmem_base + (t & 1u) * kPfN;
-        if (leader) {
-#pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk) {
-            const uint32_t off = ((kk >> 2) * L::kSubBytes + (kk & 3) * 32) >> 4;
-            umma_ss(d, desc(q_lo + off), desc(k_lo + off), idesc_qk, kk > 0);
-          }
-          umma_commit(&s_full[t & 1u]);
-        }
-        release_ring(k_ring);
-        // the last QK of the item has been issued: its Q buffer is free once it retires
-        if (j == it.n_tiles - 1 && leader) umma_commit(&q_empty[ip]);
-      };
-
-      Slim cur, nxt;
-      int round = 0;
-      bool have_cur = next_item(round, cur), have_nxt = false;
-      uint32_t t = 0;              // KV tiles issued so far (all items)
-      uint32_t item_no = 0;        // items started so far
-      uint32_t ring_base = 0;      // ring index of K_0 of the current item
-      if (have_cur) issue_qk(cur, item_no, ring_base, 0, t);
-      while (have_cur) {
-        have_nxt = next_item(round, nxt);
-        const int ip = item_no & 1;
-        const int n = cur.n_tiles;
+        const int last_pos = it.first_pos + it.rows_valid - 1;
         for (int j = 0; j < n; ++j, ++t) {
-          // one tile of look-ahead for the tensor pipe, across the item boundary too
-          if (j + 1 < n) {
-            issue_qk(cur, item_no, ring_base, j + 1, t + 1);
-          } else if (have_nxt) {
-            issue_qk(nxt, item_no + 1, ring_base + 2 * n, 0, t + 1);
-          }
-          const uint32_t v_ring = ring_base + 2 * j + 1;
-          wait_ring(v_ring);
-          if (j == n - 1) {
-            // Keys past the item's last query row are masked in P, but 0 x (stale, possibly
-            // non-finite cache contents) would still poison the row: zero those V rows.
-            const int first_dead = cur.last_pos + 1 - (cur.j0 + j) * kPfN;  // row inside the tile
-            if (first_dead < kPfN) {
-              uint8_t* vt = ring + (v_ring % kSlots) * L::kTileBytes;
-              const int vecs = (kPfN - first_dead) * 8;       // 16-byte vectors per 64-wide sub-tile
-              for (int s = 0; s < kSub; ++s)
-                for (int i = lane; i < vecs; i += 32)
-                  *reinterpret_cast<uint4*>(vt + s * L::kSubBytes + first_dead * 128 + i * 16) =
-                      make_uint4(0u, 0u, 0u, 0u);
-              fence_proxy_async_smem();
-              __syncwarp();
+          const uint32_t b = t % 3u;
+          const uint32_t slot = t % kRing;
+          if (!is_pv) {
+            // ---- S_b = Q K_t^T
+            PF_TRACE_BEGIN();
+            mbar_wait(&k_full[slot], (t / kRing) & 1, abort_flag, p.err_word);
+            PF_TRACE_END(1);
+            if (t >= 3) {     // S_b still holds P of tile t-3 until its PV has retired
+              PF_TRACE_BEGIN();
+              mbar_wait(&pv_done[b], ((t - 3) / 3u) & 1, abort_flag, p.err_word);
+              PF_TRACE_END(2);
             }
-          }
-          mbar_wait(&p_full[t & 1u], (t >> 1) & 1, abort_flag, p.err_word);
-          if (j == 0)     // O of the item two back must have been read out before it is overwritten
-            mbar_wait(&o_empty[ip], ((item_no >> 1) & 1) ^ 1, abort_flag, p.err_word);
-          tc_fence_after_sync();
-          const uint32_t p_tmem = tmem_base + (t & 1u) * kPfN;   // P over the first 64 columns of S
-          const uint32_t v_lo = (smem_u32(ring + (v_ring % kSlots) * L::kTileBytes) >> 4) | kLboV;
-          const uint32_t d = tmem_base + 256 + ip * 128;
-          if (leader) {
+            tc_fence_after_sync();
+            const uint32_t k_lo = (smem_u32(k_ring + slot * L::kTileBytes) >> 4) | kLboK;
+            const uint32_t d = tmem_base + b * kPfN;
+            if (leader) {
 #pragma unroll
-            for (int kk = 0; kk < kPfN / 16; ++kk) {
-              // A: 16 keys = 8 packed 32-bit columns per step; B: 16 keys = 2048 B further on
-              umma_ts(d, p_tmem + kk * 8, desc(v_lo + kk * (2048 >> 4)), idesc_pv,
-                      (j > 0) || (kk > 0));
+              for (int kk = 0; kk < HD / 16; ++kk) {
+                const uint32_t off = ((kk >> 2) * L::kSubBytes + (kk & 3) * 32) >> 4;
+                umma_ss(d, desc(q_lo + off), desc(k_lo + off), idesc_qk, kk > 0);
+              }
+              umma_commit(&s_full[b]);
+              // the last QK of the item has been issued: its Q buffer is free once it retires
+              if (j == n - 1) umma_commit(&q_empty[ip]);
             }
-            umma_commit(&pv_done[t & 1u]);
-            if (j == n - 1) umma_commit(&o_full[ip]);
+          } else {
+            // ---- O (+)= P_t V_t
+            uint8_t* vt = v_ring + slot * L::kTileBytes;
+            PF_TRACE_BEGIN();
+            mbar_wait(&v_full[slot], (t / kRing) & 1, abort_flag, p.err_word);
+            PF_TRACE_END(1);
+            if (j == n - 1) {
+              // Keys past the item's last query row are masked in P, but 0 x (stale, possibly
+              // non-finite cache contents) would still poison the row: zero those V rows.
+              const int first_dead = last_pos + 1 - (it.j0 + j) * kPfN;     // row inside the tile
+              if (first_dead < kPfN) {
+                const int vecs = (kPfN - first_dead) * 8;   // 16-byte vectors per 64-wide sub-tile
+                for (int s = 0; s < kSub; ++s)
+                  for (int i = lane; i < vecs; i += 32)
+                    *reinterpret_cast<uint4*>(vt + s * L::kSubBytes + first_dead * 128 + i * 16) =
+                        make_uint4(0u, 0u, 0u, 0u);
+                fence_proxy_async_smem();
+                __syncwarp();
+              }
+            }
+            PF_TRACE_BEGIN();
+            mbar_wait(&p_full[b], (t / 3u) & 1, abort_flag, p.err_word);
+            PF_TRACE_END(3);
+            if (j == 0) {   // O of the item before must have been read out before it is overwritten
+              PF_TRACE_BEGIN();
+              mbar_wait(o_empty, (item_no & 1) ^ 1, abort_flag, p.err_word);
+              PF_TRACE_END(4);
+            }
+            tc_fence_after_sync();
+            const uint32_t p_tmem = tmem_base + b * kPfN;   // P over the first 64 columns of S_b
+            const uint32_t v_lo = (smem_u32(vt) >> 4) | kLboV;
+            const uint32_t d = tmem_base + 3 * kPfN;
+            if (leader) {
+#pragma unroll
+              for (int kk = 0; kk < kPfN / 16; ++kk) {
+                // A: 16 keys = 8 packed 32-bit columns per step; B: 16 keys = 2048 B further on
+                umma_ts(d, p_tmem + kk * 8, desc(v_lo + kk * (2048 >> 4)), idesc_pv,
+                        (j > 0) || (kk > 0));
+              }
+              umma_commit(&pv_done[b]);
+            }
           }
-          release_ring(v_ring);
         }
-        ring_base += 2 * n;
         ++item_no;
-        cur = nxt;
-        have_cur = have_nxt;
       }
+#ifdef B200ATTN_PF_TRACE
+      tr_acc[7] = clock64() - tr_start;
+      tr_acc[6] = t;
+#endif
+      PF_TRACE_FLUSH(is_pv ? 5 : 2)
     }
   } else if (group <= 2) {
     // ------------------------------------------------------------------ softmax, even / odd tiles
@@ -481,28 +533,48 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t w = group - 1;                        // parity of the tiles this group takes
     const int row = (warp & 3) * 32 + lane;              // tensor-memory lane == query row
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + w * kPfN + lane_addr;
+    const uint32_t o_addr = tmem_base + 3 * kPfN + lane_addr;
     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
     uint32_t t0 = 0;                    // global index of the item's first tile
     uint32_t item_no = 0;
+    PF_TRACE_DECL
+#ifdef B200ATTN_PF_TRACE
+    const long long tr_start = clock64();
+#endif
     for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
       if (!get_item(round, it)) continue;
       const int ip = item_no & 1;
-      const uint32_t o_addr = tmem_base + 256 + ip * 128 + lane_addr;
       const int q_pos = it.first_pos + row;
       float l_run = 0.f, m_last = -INFINITY;   // this group's row sum, relative to m_last
       for (int jr = 0; jr < it.n_tiles; ++jr) {
         const uint32_t t = t0 + jr;
         if ((t & 1u) != w) continue;
-        const uint32_t k = t >> 1;                       // how many tiles of this parity came before
+        const uint32_t b = t % 3u;                       // S / P buffer of the tile
+        const uint32_t s_addr = tmem_base + b * kPfN + lane_addr;
         const int j = it.j0 + jr;                        // absolute KV tile
-        mbar_wait(&s_full[w], k & 1, abort_flag, p.err_word);
+        PF_TRACE_BEGIN();
+        mbar_wait(&s_full[b], (t / 3u) & 1, abort_flag, p.err_word);
+        PF_TRACE_END(0);
+#ifdef B200ATTN_PF_TRACE
+        const long long tr_tile = clock64();
+#endif
         tc_fence_after_sync();
+#ifdef B200ATTN_PF_NOSOFTMAX
+        if (t > 0) mbar_wait(&m_ready[w ^ 1u], (((t + 1) >> 1) - 1) & 1, abort_flag, p.err_word);
+        mbar_arrive(&m_ready[w]);
+        tc_fence_before_sync();
+        mbar_arrive(&p_full[b]);
+        continue;
+#endif
         uint32_t sreg[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
         tmem_wait_ld();
+#ifdef B200ATTN_PF_TRACE
+        const long long tr_ld = clock64();
+        tr_acc[3] += tr_ld - tr_tile;
+#endif
 
         const int key0 = j * kPfN;
         if (key0 + kPfN - 1 > it.first_pos) {   // tile crosses the diagonal for some row
@@ -531,11 +603,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           mx[c] = fmaxf(mx[c], __uint_as_float(sreg[c][31]));
         }
         const float mx_s = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+#ifdef B200ATTN_PF_TRACE
+        const long long tr_mx = clock64();
+        tr_acc[4] += tr_mx - tr_ld;
+#endif
         // running max after the tile before (the other group publishes it as soon as it has it)
         float m_prev = -INFINITY;
         if (t > 0) {
           const uint32_t other = (t + 1) >> 1;           // tiles of the other parity before t
+          PF_TRACE_BEGIN();
           mbar_wait(&m_ready[w ^ 1u], (other - 1) & 1, abort_flag, p.err_word);
+          PF_TRACE_END(1);
           if (jr > 0) m_prev = m_sh[(w ^ 1u) * kPfM + row];
         }
         float m_new = m_prev;
@@ -549,6 +627,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         // chunk goes straight back to tensor memory as 16 packed bf16x2 columns.  QK of this
         // tile has retired (s_full) and the PV that read the buffer before was issued ahead of
         // it, so the S / P columns are quiescent.
+#ifdef B200ATTN_PF_TRACE
+        const long long tr_ex = clock64();
+#endif
         const float m_sub = (WIN && m_new == -INFINITY) ? 0.f : m_new;
         const uint64_t negm2 = pack_f32x2(-m_sub, -m_sub);
         uint64_t sum2[2] = {0ull, 0ull};
@@ -560,9 +641,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             const uint64_t x2 = fma_f32x2(
                 pack_f32x2(__uint_as_float(sreg[c][kx]), __uint_as_float(sreg[c][kx + 1])), scale2,
                 negm2);
-            float x0, x1;
+            float x0, x1, e0, e1;
             unpack_f32x2(x2, x0, x1);
-            const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+            if (kPfPolyEvery > 0 && ((kx >> 1) % (kPfPolyEvery > 0 ? kPfPolyEvery : 1)) ==
+                                        (kPfPolyEvery - 1)) {
+              exp2_poly_f32x2(x0, x1, e0, e1);
+            } else {
+              e0 = fast_exp2(x0);
+              e1 = fast_exp2(x1);
+            }
             sum2[(kx >> 1) & 1] = add_f32x2(sum2[(kx >> 1) & 1], pack_f32x2(e0, e1));
             preg[kx >> 1] = pack_bf16x2(e0, e1);
           }
@@ -577,11 +664,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           l_run = l_run * f + ((a0 + a1) + (b0 + b1));
           m_last = m_new;
         }
+#ifdef B200ATTN_PF_TRACE
+        const long long tr_ex1 = clock64();
+        tr_acc[5] += tr_ex1 - tr_ex;
+#endif
         // O row rescale (rare: only when the running max moved by more than the threshold):
         // every PV up to the tile before must have retired; PV of this tile waits for p_full.
         if (__any_sync(0xffffffffu, rescale)) {
-          const uint32_t other = (t + 1) >> 1;
-          mbar_wait(&pv_done[w ^ 1u], (other - 1) & 1, abort_flag, p.err_word);
+          mbar_wait(&pv_done[(t - 1) % 3u], ((t - 1) / 3u) & 1, abort_flag, p.err_word);
           tc_fence_after_sync();
           const float corr =
               !rescale ? 1.f : ((WIN && m_prev == -INFINITY) ? 0.f : fast_exp2(m_prev - m_new));
@@ -604,28 +694,45 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&p_full[w]);
+        mbar_arrive(&p_full[b]);
+#ifdef B200ATTN_PF_TRACE
+        tr_acc[6] += clock64() - tr_ex1;
+#endif
       }
       // ---- item end: hand this group's (max, sum) of the row to the epilogue
+      PF_TRACE_BEGIN();
       mbar_wait(&stat_empty[ip], ((item_no >> 1) & 1) ^ 1, abort_flag, p.err_word);
+      PF_TRACE_END(2);
       stat_sh[(ip * 2 + w) * kPfM + row] = make_float2(m_last, l_run);
       mbar_arrive(&stat_full[ip]);
       t0 += it.n_tiles;
       ++item_no;
     }
+#ifdef B200ATTN_PF_TRACE
+    tr_acc[7] = clock64() - tr_start;
+#endif
+    if (warp == 4 || warp == 8) { PF_TRACE_FLUSH(3 + w) }
   } else {
     // ------------------------------------------------------------------ epilogue
     setmaxnreg_dec<kPfRegsEpilogue>();
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t item_no = 0;
+    uint32_t t_end = 0;                 // tiles of all items up to and including this one
+    PF_TRACE_DECL
+#ifdef B200ATTN_PF_TRACE
+    const long long tr_start = clock64();
+#endif
     for (int round = 0; round < num_rounds; ++round) {
       PrefillItem it;
       if (!get_item(round, it)) continue;
       const int ip = item_no & 1;
       const uint32_t ph = (item_no >> 1) & 1;
-      const uint32_t o_addr = tmem_base + 256 + ip * 128 + lane_addr;
+      t_end += it.n_tiles;
+      const uint32_t o_addr = tmem_base + 3 * kPfN + lane_addr;
+      PF_TRACE_BEGIN();
       mbar_wait(&stat_full[ip], ph, abort_flag, p.err_word);
+      PF_TRACE_END(0);
       const float2 s0 = stat_sh[(ip * 2 + 0) * kPfM + row];
       const float2 s1 = stat_sh[(ip * 2 + 1) * kPfM + row];
       mbar_arrive(&stat_empty[ip]);
@@ -634,7 +741,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const float l = (s0.x == -INFINITY ? 0.f : s0.y * fast_exp2(s0.x - m_fin)) +
                       (s1.x == -INFINITY ? 0.f : s1.y * fast_exp2(s1.x - m_fin));
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
-      mbar_wait(&o_full[ip], ph, abort_flag, p.err_word);
+      PF_TRACE_BEGIN();      // the PV of the item's last tile
+      mbar_wait(&pv_done[(t_end - 1) % 3u], ((t_end - 1) / 3u) & 1, abort_flag, p.err_word);
+      PF_TRACE_END(1);
+#ifdef B200ATTN_PF_TRACE
+      const long long tr_ep = clock64();
+#endif
       tc_fence_after_sync();
       __nv_bfloat16* orow =
           p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + row) * p.out_row_stride +
@@ -647,7 +759,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         tmem_wait_ld();
         if (c == HD / 16 - 1) {      // O sits in registers: hand the buffer back to the MMA warp
           tc_fence_before_sync();
-          mbar_arrive(&o_empty[ip]);
+          mbar_arrive(o_empty);
+#ifdef B200ATTN_PF_TRACE
+          tr_acc[2] += clock64() - tr_ep;
+#endif
         }
         uint32_t packed[8];
 #pragma unroll
@@ -663,6 +778,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       ++item_no;
     }
+#ifdef B200ATTN_PF_TRACE
+    tr_acc[7] = clock64() - tr_start;
+    tr_acc[6] = item_no;
+#endif
+    (void)item_no;
   }
 
   tc_fence_before_sync();

@@ -213,6 +213,27 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
+// 2^x for two values on the FMA and integer pipes (no MUFU).  x = n + f with n = round(x) taken
+// by the add-a-large-constant trick (n lands in the low mantissa bits of t), 2^f by a cubic
+// fitted on [-0.5, 0.5] (max relative error 1.0e-4), and n added to the exponent field.
+// x is clamped at -126 (the result is then ~1e-38, i.e. zero for a softmax weight); x must stay
+// below 127.
+__device__ __forceinline__ void exp2_poly_f32x2(float x0, float x1, float& e0, float& e1) {
+  const uint64_t x2 = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t t2 = add_f32x2(x2, pack_f32x2(12582912.f, 12582912.f));
+  const uint64_t n2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t p2 = fma_f32x2(pack_f32x2(0.05500893f, 0.05500893f), f2,
+                          pack_f32x2(0.24221095f, 0.24221095f));
+  p2 = fma_f32x2(p2, f2, pack_f32x2(0.69328290f, 0.69328290f));
+  p2 = fma_f32x2(p2, f2, pack_f32x2(1.f, 1.f));
+  float p0, p1, t0, t1;
+  unpack_f32x2(p2, p0, p1);
+  unpack_f32x2(t2, t0, t1);
+  e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+
 // ---------------------------------------------------------------- tcgen05 (prefill path)
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
