@@ -136,3 +136,44 @@ def test_error_watch_reports_a_bad_page_id_one_poll_later():
         watch.poll()
     assert ops.read_error_word() == 0 and float(kc.abs().sum()) == 0
     watch.poll()
+
+
+def test_layer_wrapper_rotary_writes_the_cache_in_the_same_launch(clean_error_word):
+    """A layer built with rotary_dim gets positions: q and k are rotated in place and, because the
+    step's metadata carries a slot mapping, the rotated k and v land in the cache in that one
+    launch; the Impl then only attends.  Checked against the rotary restatement followed by the
+    oracle's forward (rotation arithmetic as the plugin's rotary layer does it: within 2 bf16 ulps
+    of the CPU statement, so the comparison of the attention uses the usual budget and the cache
+    is compared with the rotated k the launch returned)."""
+    from b200attn import B200Attention, B200AttentionMetadataBuilder, sharding
+
+    g = torch.Generator().manual_seed(23)
+    nq, nkv, hd, bs, n, width = 8, 2, 128, 64, 4, 6
+    bt = (torch.randperm(n * width, generator=g) + 1).reshape(n, width).int()
+    computed = torch.randint(1, width * bs - 2, (n,), generator=g).int()
+    sched = torch.ones(n, dtype=torch.int32)
+    nb = n * width + 1
+    layer = B200Attention(nq, hd, hd ** -0.5, num_kv_heads=nkv, rotary_dim=hd, rope_theta=500000.0)
+    caches = sharding.allocate_kv_caches(["attn"], nb, nkv, bs, hd, device="cuda")
+    sharding.bind_kv_caches({"attn": layer}, caches)
+    kc0, vc0 = randn_bf16((nb, nkv, bs, hd), g), randn_bf16((nb, nkv, bs, hd), g)
+    caches["attn"][0].copy_(kc0)
+    caches["attn"][1].copy_(vc0)
+    state = B200AttentionMetadataBuilder(device=torch.device("cuda")).device_step_state(
+        n, width, bs, tokens_per_row=1)
+    meta = state.build(computed.cuda(), sched.cuda(), bt.cuda())
+    q, k, v = (randn_bf16((n, h * hd), g) for h in (nq, nkv, nkv))
+    positions = computed.long()                      # the new token's position
+    dq, dk = q.cuda(), k.cuda()
+    out = layer(dq, dk, v.cuda(), attn_metadata=meta, positions=positions.cuda())
+    assert layer.impl.kv_written_upstream is False    # consumed by the forward
+
+    want_q, want_k = restate.rotary_embedding(positions, q, k, layer.inv_freq.cpu(), hd, hd)
+    for got, want in ((dq.cpu(), want_q), (dk.cpu(), want_k)):    # rotated in place
+        assert (got.float() - want.float()).abs().max() <= 2 * 2.0 ** -7 * want.float().abs().max()
+    rot_q, rot_k = dq.cpu(), dk.cpu()
+    want_out, want_kc, want_vc = restate.impl_forward(
+        rot_q, rot_k, v, kc0, vc0, num_heads=nq, num_kv_heads=nkv, head_size=hd, scale=hd ** -0.5,
+        num_users=n, cache_position=computed, page_table=bt, compute_dtype=torch.float32)
+    assert torch.equal(caches["attn"][0].cpu(), want_kc) and torch.equal(caches["attn"][1].cpu(), want_vc)
+    assert_attention_close(out, want_out, "rotary + cache write + decode")

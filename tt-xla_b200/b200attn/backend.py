@@ -428,6 +428,9 @@ class B200AttentionBackendImpl:
             raise NotImplementedError("logits_soft_cap is not supported")
         self.sinks = sinks
         self._sinks_f32 = None   # ((device, data_ptr, version), fp32 copy)
+        # Set by a caller that has already written this step's K / V rows into the cache (the
+        # fused rotary + cache write of B200Attention); consumed by the next forward.
+        self.kv_written_upstream = False
         if self.sinks is not None:
             assert self.sinks.shape[0] == num_heads, (
                 "Sinks must have the same number of heads as the number of "
@@ -465,13 +468,15 @@ class B200AttentionBackendImpl:
         if output_scale is not None or output_block_scale is not None:
             raise NotImplementedError("fused output quantisation is not supported")
         kv_pair = self._split_kv_cache(kv_cache)
+        written, self.kv_written_upstream = self.kv_written_upstream, False
         if attn_metadata.is_varlen:
-            self._forward_varlen(query, key, value, kv_pair, attn_metadata, output)
+            self._forward_varlen(query, key, value, kv_pair, attn_metadata, output,
+                                 writes_cache=not written)
             return output
 
         inputs = self._prepare_inputs(query, key, value, attn_metadata)
         has_cache = kv_pair is not None
-        writes_cache = has_cache and self.kv_sharing_target_layer_name is None
+        writes_cache = has_cache and self.kv_sharing_target_layer_name is None and not written
         if inputs.is_prefill:
             if writes_cache:
                 self._handle_paged_attention(inputs, kv_pair, attn_metadata)
@@ -592,7 +597,8 @@ class B200AttentionBackendImpl:
         )
 
     # ------------------------------------------------------------------ vLLM varlen form
-    def _forward_varlen(self, query, key, value, kv_pair, md: B200Metadata, output) -> None:
+    def _forward_varlen(self, query, key, value, kv_pair, md: B200Metadata, output,
+                        writes_cache: bool = True) -> None:
         if kv_pair is None:
             # Memory-profiling run before the cache exists: nothing to attend to.
             output.zero_()
@@ -602,7 +608,7 @@ class B200AttentionBackendImpl:
         q = query[:n_tok].reshape(n_tok, nq, hd)
         out = output[:n_tok].reshape(n_tok, nq, hd)
         nd = md.num_decodes
-        writes_cache = self.kv_sharing_target_layer_name is None
+        writes_cache = writes_cache and self.kv_sharing_target_layer_name is None
         # A pure decode batch writes its new rows inside the decode launch (a row's slot is
         # block_table[pos // bs] * bs + pos % bs, which is what that launch computes; padding
         # rows carry position -1 and are skipped like slot -1); mixed batches scatter by slot.
@@ -660,8 +666,18 @@ class B200Attention(torch.nn.Module):
     metadata (`set_metadata`, or the `attn_metadata` argument)."""
 
     def __init__(self, num_heads: int, head_size: int, scale: float,
-                 num_kv_heads: Optional[int] = None, **impl_kwargs) -> None:
+                 num_kv_heads: Optional[int] = None, *, rotary_dim: Optional[int] = None,
+                 rope_theta: float = 10000.0, **impl_kwargs) -> None:
         super().__init__()
+        # NeoX-style rotary embedding applied by the layer itself when `forward` is given
+        # positions (the plugin's rotary layer, layers/rotary_embedding.py:51-66): one launch
+        # rotates q and k in place and, when the step's metadata carries a slot mapping, also
+        # writes the rotated k and v into the cache, so the Impl skips its own cache write.
+        self.rotary_dim = rotary_dim
+        self.inv_freq = None
+        if rotary_dim is not None:
+            self.inv_freq = 1.0 / (rope_theta ** (
+                torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
         self.num_heads = num_heads
         self.head_size = self.head_size_v = head_size
         self.num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
@@ -679,15 +695,37 @@ class B200Attention(torch.nn.Module):
     def set_metadata(self, attn_metadata: B200Metadata) -> None:
         self.attn_metadata = attn_metadata
 
+    def _rotate_and_write(self, q2, k2, v2, positions, md) -> None:
+        """q2 / k2 rotated in place; with a slot mapping in the metadata and a cache of its own
+        the same launch writes k and v, and the Impl is told so."""
+        if self.inv_freq.device != q2.device:
+            self.inv_freq = self.inv_freq.to(q2.device)
+        kv_pair = self.impl._split_kv_cache(self.kv_cache)
+        slots = getattr(md, "slot_mapping", None)
+        fused_write = (kv_pair is not None and slots is not None
+                       and self.impl.kv_sharing_target_layer_name is None
+                       and kv_pair[0].dtype == torch.bfloat16)
+        ops.rope_kv_scatter_slots(
+            q2, k2, v2 if fused_write else None, positions.reshape(-1).to(torch.int64),
+            self.inv_freq, self.rotary_dim, self.head_size,
+            kv_pair[0] if fused_write else None, kv_pair[1] if fused_write else None,
+            slots[: q2.shape[0]] if fused_write else None)
+        self.impl.kv_written_upstream = fused_write
+
     def forward(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                 output_shape: Optional[torch.Size] = None,
-                attn_metadata: Optional[B200Metadata] = None) -> torch.Tensor:
+                attn_metadata: Optional[B200Metadata] = None,
+                positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         q2 = flatten_heads(query, "query", self.num_heads, self.head_size)
         k2 = flatten_heads(key, "key", self.num_kv_heads, self.head_size)
         v2 = flatten_heads(value, "value", self.num_kv_heads, self.head_size_v)
         out = torch.empty(output_shape if output_shape is not None else q2.shape,
                           dtype=q2.dtype, device=q2.device)
         md = attn_metadata if attn_metadata is not None else self.attn_metadata
+        if positions is not None:
+            if self.inv_freq is None:
+                raise ValueError("positions given to a layer built without rotary_dim")
+            self._rotate_and_write(q2, k2, v2, positions, md)
         self.impl.forward(self, q2, k2, v2, self.kv_cache, md, output=out.view(q2.shape[0], -1))
         if out.numel() != query.numel():
             raise ValueError(

@@ -88,10 +88,45 @@ static int get_device(DeviceInfo** out) {
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// A serving loop encodes the same few tensor maps step after step (the caches and activation
+// buffers keep their addresses): the last few encodings are kept per host thread.
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols, row_stride;
+  uint32_t box_rows, kind;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && row_stride == o.row_stride &&
+           box_rows == o.box_rows && kind == o.kind;
+  }
+};
+constexpr int kMapCacheSize = 16;
+struct MapCache {
+  MapKey keys[kMapCacheSize];
+  CUtensorMap maps[kMapCacheSize];
+  int used = 0, next = 0;
+  bool find(const MapKey& k, CUtensorMap* out) const {
+    for (int i = 0; i < used; ++i)
+      if (keys[i] == k) {
+        *out = maps[i];
+        return true;
+      }
+    return false;
+  }
+  void put(const MapKey& k, const CUtensorMap& m) {
+    keys[next] = k;
+    maps[next] = m;
+    next = (next + 1) % kMapCacheSize;
+    if (used < kMapCacheSize) ++used;
+  }
+};
+static thread_local MapCache t_map_cache;
+
 // bf16 matrix [rows, cols] with `row_stride` elements between rows; boxes of
 // [box_rows x 64 columns] land in shared memory with the 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                     uint64_t row_stride, uint32_t box_rows) {
+  const MapKey key{base, rows, cols, row_stride, box_rows, 0u};
+  if (t_map_cache.find(key, map)) return B200ATTN_OK;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {row_stride * 2};
   const cuuint32_t box[2] = {64, box_rows};
@@ -100,11 +135,15 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ERR_TENSOR_MAP;
+  if (r != CUDA_SUCCESS) return B200ATTN_ERR_TENSOR_MAP;
+  t_map_cache.put(key, *map);
+  return B200ATTN_OK;
 }
 
 // e4m3 cache [rows, 128] (one byte per element): boxes of [box_rows x 128 bytes], 128-byte swizzle.
 static int make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows) {
+  const MapKey key{base, rows, 128, 128, box_rows, 1u};
+  if (t_map_cache.find(key, map)) return B200ATTN_OK;
   const cuuint64_t dims[2] = {128, rows};
   const cuuint64_t strides[1] = {128};
   const cuuint32_t box[2] = {128, box_rows};
@@ -113,7 +152,21 @@ static int make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint32
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ERR_TENSOR_MAP;
+  if (r != CUDA_SUCCESS) return B200ATTN_ERR_TENSOR_MAP;
+  t_map_cache.put(key, *map);
+  return B200ATTN_OK;
+}
+
+// The opt-in to more than 48 KiB of dynamic shared memory is a per-kernel, per-device setting:
+// made once, not before every launch.
+template <typename Kernel>
+static cudaError_t allow_dynamic_smem(Kernel kern, int bytes, bool* done_for_device) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (done_for_device[dev]) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done_for_device[dev] = true;
+  return e;
 }
 
 static int check_cache_geometry(int num_kv_heads, int head_size, int block_size,
@@ -184,8 +237,8 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
                          int num_users, cudaStream_t s) {
   using L = DecodeSmem<HD, BS, STAGES>;
   auto kern = paged_decode_splitkv_kernel<HD, BS, STAGES>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  static bool smem_allowed[kMaxDevices] = {};
+  cudaError_t e = allow_dynamic_smem(kern, L::kTotalBytes, smem_allowed);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(p.num_splits, p.num_kv_heads, num_users);
   kern<<<grid, kDecThreads, L::kTotalBytes, s>>>(tk, tv, p);
@@ -204,8 +257,8 @@ static int launch_decode_fp8(const CUtensorMap& tk, const CUtensorMap& tv, const
                              int num_users, cudaStream_t s) {
   using L = DecodeFp8Smem<BS, STAGES>;
   auto kern = paged_decode_fp8_kernel<BS, STAGES>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  static bool smem_allowed[kMaxDevices] = {};
+  cudaError_t e = allow_dynamic_smem(kern, L::kTotalBytes, smem_allowed);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(p.num_splits, p.num_kv_heads, num_users);
   kern<<<grid, kDecThreads, L::kTotalBytes, s>>>(tk, tv, p);
@@ -224,8 +277,8 @@ static int launch_prefill_win(const CUtensorMap& tq, const CUtensorMap& tk, cons
                               const PrefillParams& p, int sm_count, cudaStream_t s) {
   using L = PrefillSmem<HD>;
   auto kern = prefill_tcgen05_kernel<HD, BS, WIN>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  static bool smem_allowed[kMaxDevices] = {};
+  cudaError_t e = allow_dynamic_smem(kern, L::kTotalBytes, smem_allowed);
   if (e != cudaSuccess) return static_cast<int>(e);
   // persistent: one CTA per SM (the kernel holds all of an SM's shared and tensor memory)
   dim3 grid(static_cast<unsigned>(p.total_items < sm_count ? p.total_items : sm_count));
@@ -247,8 +300,8 @@ static int launch_rowlinear(const CUtensorMap& tw, const CUtensorMap& tx, const 
                             int tiles, cudaStream_t s) {
   using L = RowLinearSmem<NB>;
   auto kern = rowlinear_allreduce_kernel<NB, S>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+  static bool smem_allowed[kMaxDevices] = {};
+  cudaError_t e = allow_dynamic_smem(kern, L::kTotalBytes, smem_allowed);
   if (e != cudaSuccess) return static_cast<int>(e);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(S, static_cast<unsigned>(tiles), 1);
