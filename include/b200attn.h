@@ -319,6 +319,24 @@ size_t b200attn_decode_workspace_bytes(int num_users, int num_q_heads, int head_
                                        int num_splits);
 
 /* ------------------------------------------------------------------------------------------
+ * Chunked prefill over an fp8 (e4m3) cache, step 1: widen the pages the batch reads.
+ * Replaces: nothing of its own -- it is what lets b200attn_prefill (kv_is_paged = 1) stand in
+ *           for torch.ops.tt.chunked_scaled_dot_product_attention (custom_ops.py:1334-1443) when
+ *           the plugin's cache dtype is float8_e4m3fn (attention.py:42-51, 692-700).
+ * For every sequence s and page slot i below ceil((q_start[s] + q_len[s]) / block_size), page
+ * page_table[s, i] of both caches is copied, widened to bf16 (exact), into page s * width + i
+ * of k_dst / v_dst, which must hold num_seqs * page_table_width pages of
+ * [num_kv_heads, block_size, head_size] bf16 each.  Then call b200attn_prefill with k_dst /
+ * v_dst as the caches, the identity page table (entry [s, i] = s * width + i) and
+ * num_blocks = num_seqs * page_table_width.  Scratch and identity table are the caller's.
+ * ------------------------------------------------------------------------------------------ */
+int b200attn_dequant_pages_fp8(void* k_dst, void* v_dst, const void* k_cache, const void* v_cache,
+                               const int32_t* page_table, int64_t page_table_stride,
+                               int page_table_width, const int32_t* cu_q, const int32_t* q_start,
+                               int num_seqs, int num_kv_heads, int head_size, int block_size,
+                               int64_t num_blocks, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Causal varlen prefill / chunked-prefill attention on tcgen05 tensor cores.
  * Replaces: torch.ops.tt.scaled_dot_product_attention with is_causal=True, attn_mask=None
  *           (custom_ops.py:635-742; call site attention.py:575-598)            [kv_is_paged = 0]

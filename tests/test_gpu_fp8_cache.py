@@ -167,10 +167,6 @@ def test_fp8_needs_head_size_128_and_matching_caches():
     with pytest.raises(ValueError, match="both"):
         ops.paged_decode(q, kc, kc.to(torch.bfloat16), pt,
                          torch.zeros(1, dtype=torch.int32, device="cuda"))
-    kc128 = torch.zeros(4, 2, 32, 128, device="cuda").to(FP8)
-    with pytest.raises(NotImplementedError, match="fp8"):
-        ops.prefill(torch.zeros(32, 8, 128, dtype=torch.bfloat16, device="cuda"), kc128, kc128,
-                    torch.tensor([0, 32], dtype=torch.int32), page_table=pt)
 
 
 def test_impl_forward_fp8_cache(clean_error_word):
@@ -213,11 +209,63 @@ def test_impl_forward_fp8_cache(clean_error_word):
         num_users=users, cache_position=pos, page_table=pt, compute_dtype=torch.float32)
     assert torch.equal(_bits(kd.cpu()), _bits(kc_1)) and torch.equal(_bits(vd.cpu()), _bits(vc_1))
     assert_attention_close(out1.cpu(), want1, "fp8 impl decode")
-    with pytest.raises(NotImplementedError, match="fp8"):
-        md2 = B200Metadata(cache_position=torch.tensor([T + 63, T + 63], dtype=torch.int32).cuda(),
-                           page_table=pt.cuda(), num_users=users,
-                           chunk_start_idx=torch.tensor([T], dtype=torch.int32).cuda(),
-                           batch_idx=torch.arange(users, dtype=torch.int32, device="cuda"),
-                           fill_page_table=torch.roll(pt, -2, dims=1).contiguous().cuda())
-        impl.forward(None, q[: users * 64].cuda(), k[: users * 64].cuda(), v[: users * 64].cuda(),
-                     [kd, vd], md2, output=out[: users * 64])
+    # a chunk of 64 tokens on top of the T-token prefix, attended over the fp8 pages
+    # (chunked prefill: attention.py:545-560)
+    n = users * 64
+    md2 = B200Metadata(cache_position=torch.tensor([T + 63, T + 63], dtype=torch.int32).cuda(),
+                       page_table=pt.cuda(), num_users=users,
+                       chunk_start_idx=torch.tensor([T], dtype=torch.int32).cuda(),
+                       batch_idx=torch.arange(users, dtype=torch.int32, device="cuda"),
+                       fill_page_table=torch.roll(pt, -2, dims=1).contiguous().cuda())
+    # decode step above wrote position T of user 0 and 70 of user 1; start from the prefill state
+    kd, vd = kc_o.cuda(), vc_o.cuda()
+    impl.forward(None, q[:n].cuda(), k[:n].cuda(), v[:n].cuda(), [kd, vd], md2, output=out[:n])
+    want2, kc_2, vc_2 = restate.impl_forward(
+        q[:n], k[:n], v[:n], kc_o, vc_o, num_heads=nq, num_kv_heads=nkv, head_size=hd,
+        scale=hd ** -0.5, num_users=users,
+        cache_position=torch.tensor([T + 63, T + 63], dtype=torch.int32), page_table=pt,
+        fill_page_table=torch.roll(pt, -2, dims=1).contiguous(), batch_idx=torch.arange(users),
+        chunk_start_idx=torch.tensor([T], dtype=torch.int32), compute_dtype=torch.float32)
+    assert torch.equal(_bits(kd.cpu()), _bits(kc_2)) and torch.equal(_bits(vd.cpu()), _bits(vc_2))
+    assert_attention_close(out[:n].cpu(), want2, "fp8 impl chunked prefill")
+
+
+@pytest.mark.parametrize("bs", [32, 64])
+def test_chunked_prefill_over_fp8_pages(bs, clean_error_word):
+    """Ragged sequences with different prefixes over an e4m3 cache: the pages each sequence reads
+    are widened (exactly) into a bf16 pool and attended there; expected = the oracle's chunked op
+    on the same e4m3 values in fp32.  Unwidened slots of the pool hold NaN to show they are never
+    read into a result."""
+    from b200attn import ops
+
+    g = torch.Generator().manual_seed(70 + bs)
+    nq, nkv, hd = 8, 2, 128
+    q_lens = [1, 37, 128, 200]
+    starts = [300, 64, 0, 128]
+    nblks = [(s + t + bs - 1) // bs for s, t in zip(starts, q_lens)]
+    width = max(nblks) + 2
+    nb = sum(nblks) + 1
+    perm = torch.randperm(nb - 1, generator=g) + 1
+    pt = torch.zeros(len(q_lens), width, dtype=torch.int32)
+    o = 0
+    for i, n_ in enumerate(nblks):
+        pt[i, :n_] = perm[o:o + n_].int()
+        o += n_
+    kc = restate.quantize_kv_fp8(randn_bf16((nb, nkv, bs, hd), g))
+    vc = restate.quantize_kv_fp8(randn_bf16((nb, nkv, bs, hd), g))
+    total = sum(q_lens)
+    q = randn_bf16((total, nq, hd), g)
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    # poison a scratch pool of the size the op will ask for, so stale contents would show
+    ops._fp8_scratch.clear()
+    out = ops.prefill(q.cuda(), kc.cuda(), vc.cuda(), cu_q, scale=hd ** -0.5, page_table=pt.cuda(),
+                      q_start=torch.tensor(starts, dtype=torch.int32).cuda())
+    for pool in list(ops._fp8_scratch.values())[0][:2]:
+        pool.fill_(float("nan"))
+    out = ops.prefill(q.cuda(), kc.cuda(), vc.cuda(), cu_q, scale=hd ** -0.5, page_table=pt.cuda(),
+                      q_start=torch.tensor(starts, dtype=torch.int32).cuda()).cpu()
+    for i, (t, s_) in enumerate(zip(q_lens, starts)):
+        qi = q[cu_q[i]:cu_q[i + 1]].transpose(0, 1)[None].float()
+        want = restate.chunked_sdpa(qi, kc.float(), vc.float(), pt[i:i + 1, :nblks[i]], s_,
+                                    hd ** -0.5)[0].transpose(0, 1)
+        assert_attention_close(out[cu_q[i]:cu_q[i + 1]], want, f"seq {i}")

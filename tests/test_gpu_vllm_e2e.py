@@ -40,13 +40,23 @@ def run_worker(backend: str, workdir: str, extra=()) -> dict:
 
 
 @pytest.fixture(scope="module")
-def runs(tmp_path_factory):
+def workdir(tmp_path_factory):
     pytest.importorskip("vllm")
     pytest.importorskip("transformers")
-    workdir = str(tmp_path_factory.mktemp("vllm_e2e"))
-    subprocess.run([sys.executable, WORKER, "--prepare", "--workdir", workdir], check=True,
+    path = str(tmp_path_factory.mktemp("vllm_e2e"))
+    subprocess.run([sys.executable, WORKER, "--prepare", "--workdir", path], check=True,
                    stdin=subprocess.DEVNULL, capture_output=True, timeout=600)
-    return run_worker("custom", workdir), run_worker("stock", workdir)
+    return path
+
+
+@pytest.fixture(scope="module")
+def custom_run(workdir):
+    return run_worker("custom", workdir)
+
+
+@pytest.fixture(scope="module")
+def runs(workdir, custom_run):
+    return custom_run, run_worker("stock", workdir)
 
 
 def test_prompt_logprobs_match_the_stock_backend(runs):
@@ -82,3 +92,18 @@ def test_greedy_tokens_match_the_stock_backend(runs):
             break
         else:
             assert agree >= MIN_LEADING_TOKENS
+
+
+def test_fp8_kv_cache_through_vllm(workdir, custom_run):
+    """The same model with `kv_cache_dtype="fp8"` (unscaled e4m3 pages, as the plugin stores them,
+    attention.py:42-51, 692-700): vLLM hands the cache over as raw bytes, chunked prefill attends
+    over widened pages, decode streams the e4m3 pages.  Against this backend's own bf16-cache run
+    the prompt log-probabilities may differ only by the quantisation of K and V."""
+    fp8 = run_worker("custom", workdir, ("--kv-cache-dtype", "fp8"))
+    total, n = 0.0, 0
+    for c, s in zip(fp8["results"], custom_run["results"]):
+        assert len(c["tokens"]) == len(s["tokens"])
+        for a, b in zip(c["prompt_logprobs"], s["prompt_logprobs"]):
+            total += abs(a - b)
+            n += 1
+    assert n > 800 and total / n <= 0.05, f"mean |d logprob| {total / n:.4f}"

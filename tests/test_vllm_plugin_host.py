@@ -24,7 +24,7 @@ def test_register_points_custom_at_this_backend(monkeypatch):
     assert sorted(B.get_supported_kernel_block_sizes()) == [32, 64]
     assert sorted(B.get_supported_head_sizes()) == [64, 128]
     assert B.accept_output_buffer and B.forward_includes_kv_cache_update
-    assert B.supported_kv_cache_dtypes == ["auto", "bfloat16"]
+    assert B.supported_kv_cache_dtypes == ["auto", "bfloat16", "fp8", "fp8_e4m3"]
 
 
 def test_impl_accepts_vllm_constructor_arguments():

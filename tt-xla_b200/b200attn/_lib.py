@@ -42,6 +42,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int,
          c_int64, c_int, c_void_p],
     ),
+    "b200attn_dequant_pages_fp8": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+         c_int, c_int, c_int, c_int, c_int64, c_void_p],
+    ),
     "b200attn_build_step_metadata": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,

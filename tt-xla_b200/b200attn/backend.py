@@ -236,7 +236,7 @@ class B200AttentionBackend:
     accept_output_buffer = True
     forward_includes_kv_cache_update = True
     supported_dtypes = [torch.bfloat16]
-    supported_kv_cache_dtypes = ["auto", "bfloat16"]
+    supported_kv_cache_dtypes = ["auto", "bfloat16", "fp8", "fp8_e4m3"]   # fp8: head_size 128
     supported_head_sizes = [64, 128]
     supported_block_sizes = [32, 64]
 
@@ -489,17 +489,22 @@ class B200AttentionBackendImpl:
                                            write_new_token=writes_cache)
         return output
 
-    @staticmethod
-    def _split_kv_cache(kv_cache):
+    def _split_kv_cache(self, kv_cache):
         """[k_cache, v_cache] (the reference's form, model_runner.py:4603-4609), or vLLM's single
-        [2, nb, nkv, bs, hd] tensor; None while profiling with a placeholder."""
+        [2, nb, nkv, bs, hd] tensor; None while profiling with a placeholder.  An engine that
+        stores an fp8 cache as raw bytes (vLLM allocates uint8) gets the e4m3 view the kernels
+        and the plugin's dtype map (attention.py:42-51) mean."""
+        pair = None
         if isinstance(kv_cache, (list, tuple)):
             if len(kv_cache) >= 2 and kv_cache[0].numel() > 0:
-                return kv_cache[0], kv_cache[1]
-            return None
-        if isinstance(kv_cache, torch.Tensor) and kv_cache.dim() == 5 and kv_cache.shape[0] == 2:
-            return kv_cache[0], kv_cache[1]
-        return None
+                pair = (kv_cache[0], kv_cache[1])
+        elif isinstance(kv_cache, torch.Tensor) and kv_cache.dim() == 5 and kv_cache.shape[0] == 2:
+            pair = (kv_cache[0], kv_cache[1])
+        if pair is not None and self.kv_cache_quantized_dtype is not None \
+                and pair[0].dtype == torch.uint8:
+            pair = (pair[0].view(self.kv_cache_quantized_dtype),
+                    pair[1].view(self.kv_cache_quantized_dtype))
+        return pair
 
     def _prepare_inputs(self, query, key, value, attn_metadata: B200Metadata) -> PluginBatch:
         """Shapes the three activations by user (what attention.py:381-459 hands its ops)."""

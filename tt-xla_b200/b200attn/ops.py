@@ -385,10 +385,6 @@ def prefill(
     paged = page_table is not None
     if paged:
         nb, nkv, bs, _hd = _check_cache(k_src, v_src)
-        if k_src.dtype == torch.float8_e4m3fn:
-            raise NotImplementedError(
-                "prefill over an fp8 paged cache is not implemented (decode and the cache writes "
-                "are); prefill the fresh bf16 K/V instead")
         if _hd != hd:
             raise ValueError("cache head_size differs from query head_size")
         _i32(page_table, "page_table")
@@ -419,6 +415,11 @@ def prefill(
     if cu_q is None:
         cu_q = cu_q_host.to(query.device, non_blocking=True)
     _i32(cu_q, "cu_q")
+    if paged and k_src.dtype == torch.float8_e4m3fn:
+        # The tcgen05 kernel takes 16-bit tiles: widen the pages this batch reads into a bf16
+        # scratch pool laid out [sequence][page slot] and attend over that through the identity
+        # page table.  e4m3 -> bf16 is exact, so the kernel sees the cache's own values.
+        k, v, page_table, nb = _widen_fp8_pages(k_src, v_src, page_table, cu_q, q_start, num_seqs)
     if out is None:
         out_t = torch.empty((total_q, nq, hd), dtype=torch.bfloat16, device=query.device)
     else:
@@ -445,6 +446,41 @@ def prefill(
         ),
     )
     return out if out is not None else out_t
+
+
+_fp8_scratch: dict[tuple, tuple] = {}
+
+
+def _widen_fp8_pages(k_cache, v_cache, page_table, cu_q, q_start, num_seqs):
+    """bf16 copies of the pages `page_table[:num_seqs]` lists for an e4m3 cache pair; returns
+    (k_pool, v_pool, identity page table, pool size in pages).  The scratch is cached per
+    (device, stream) and grown on demand; torch owns it."""
+    nb, nkv, bs, hd = k_cache.shape
+    width = page_table.shape[1]
+    pages = num_seqs * width
+    dev = k_cache.device
+    key = (dev.index or 0, torch.cuda.current_stream(dev).cuda_stream, nkv, bs, hd)
+    have = _fp8_scratch.get(key)
+    if have is None or have[0].shape[0] < pages:
+        grow = max(pages, 2 * have[0].shape[0] if have is not None else 0)
+        have = (torch.empty((grow, nkv, bs, hd), dtype=torch.bfloat16, device=dev),
+                torch.empty((grow, nkv, bs, hd), dtype=torch.bfloat16, device=dev), {})
+        _fp8_scratch[key] = have
+    k_pool, v_pool, tables = have
+    ident = tables.get((num_seqs, width))
+    if ident is None:
+        ident = torch.arange(pages, dtype=torch.int32, device=dev).reshape(num_seqs, width)
+        tables[(num_seqs, width)] = ident
+    _lib.check(
+        "b200attn_dequant_pages_fp8",
+        _lib.lib().b200attn_dequant_pages_fp8(
+            k_pool.data_ptr(), v_pool.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            page_table.data_ptr(), page_table.stride(0), width, cu_q.data_ptr(),
+            q_start.data_ptr() if q_start is not None else None, num_seqs, nkv, hd, bs, nb,
+            torch.cuda.current_stream(dev).cuda_stream,
+        ),
+    )
+    return k_pool, v_pool, ident, k_pool.shape[0]
 
 
 def read_error_word(device: Optional[torch.device] = None) -> int:

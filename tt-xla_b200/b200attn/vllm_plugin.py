@@ -65,7 +65,8 @@ class B200VllmAttentionBackend(AttentionBackend):
     accept_output_buffer = True
     forward_includes_kv_cache_update = True
     supported_dtypes = [torch.bfloat16]
-    supported_kv_cache_dtypes = ["auto", "bfloat16"]
+    # fp8 = unscaled e4m3, as the plugin stores it (attention.py:42-51, 692-700); head_size 128
+    supported_kv_cache_dtypes = ["auto", "bfloat16", "fp8", "fp8_e4m3"]
 
     @staticmethod
     def get_name() -> str:

@@ -472,6 +472,42 @@ int b200attn_kv_scatter_slots_ex(void* k_cache, void* v_cache, const void* k_new
   return launch_scatter(kScatterSlots, p, head_size, stream);
 }
 
+int b200attn_dequant_pages_fp8(void* k_dst, void* v_dst, const void* k_cache, const void* v_cache,
+                               const int32_t* page_table, int64_t page_table_stride,
+                               int page_table_width, const int32_t* cu_q, const int32_t* q_start,
+                               int num_seqs, int num_kv_heads, int head_size, int block_size,
+                               int64_t num_blocks, void* stream) {
+  if (!k_dst || !v_dst || !k_cache || !v_cache || !page_table || !cu_q)
+    return B200ATTN_ERR_NULL_POINTER;
+  if (num_seqs < 0 || page_table_width <= 0) return B200ATTN_ERR_BAD_ARGUMENT;
+  if (int rc = check_cache_geometry(num_kv_heads, head_size, block_size, num_blocks)) return rc;
+  if (!aligned16(k_dst) || !aligned16(v_dst) || !aligned16(k_cache) || !aligned16(v_cache))
+    return B200ATTN_ERR_MISALIGNED;
+  if (static_cast<int64_t>(num_seqs) * page_table_width * num_kv_heads * block_size > 0x7fffffffLL)
+    return B200ATTN_ERR_TOO_LARGE;
+  if (num_seqs > 65535) return B200ATTN_ERR_TOO_LARGE;
+  DeviceInfo* dev;
+  if (int rc = get_device(&dev)) return rc;
+  if (num_seqs == 0) return B200ATTN_OK;
+  DequantPagesParams p{};
+  p.k_src = static_cast<const uint8_t*>(k_cache);
+  p.v_src = static_cast<const uint8_t*>(v_cache);
+  p.k_dst = static_cast<__nv_bfloat16*>(k_dst);
+  p.v_dst = static_cast<__nv_bfloat16*>(v_dst);
+  p.page_table = page_table;
+  p.page_table_stride = page_table_stride;
+  p.page_table_width = page_table_width;
+  p.cu_q = cu_q;
+  p.q_start = q_start;
+  p.block_size = block_size;
+  p.page_elems = num_kv_heads * block_size * head_size;
+  p.num_blocks = num_blocks;
+  p.err_word = dev->err_word;
+  dim3 grid(static_cast<unsigned>(page_table_width), static_cast<unsigned>(num_seqs));
+  dequant_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int b200attn_build_step_metadata(const int32_t* num_computed, const int32_t* num_scheduled,
                                  const int32_t* block_table, int64_t block_table_stride,
                                  int num_requests, int rows, int page_table_width,

@@ -115,4 +115,66 @@ __global__ void __launch_bounds__(256) kv_scatter_kernel(const ScatterParams p) 
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Widening of the pages a prefill batch reads from an e4m3 cache into a bf16 page pool.
+//
+// The tcgen05 prefill kernel takes 16-bit K / V tiles.  Over an fp8 cache the prefix pages of
+// the batch's sequences are first copied, widened, into a compact scratch pool laid out
+// [sequence][page slot] (slot i of sequence s = page_table[s, i]), and the kernel then reads that
+// pool through the identity page table.  Every e4m3 value is exactly representable in bf16, so
+// the attention sees exactly the cache's values.  HBM-bound: 1 byte read + 2 written per element
+// of the context; the attention over it is tensor-bound and an order of magnitude longer.
+struct DequantPagesParams {
+  const uint8_t* k_src;       // [num_blocks, nkv, bs, hd] e4m3
+  const uint8_t* v_src;
+  __nv_bfloat16* k_dst;       // [num_seqs * width, nkv, bs, hd] bf16
+  __nv_bfloat16* v_dst;
+  const int32_t* page_table;
+  int64_t page_table_stride;
+  int page_table_width;
+  const int32_t* cu_q;        // [num_seqs + 1]
+  const int32_t* q_start;     // [num_seqs] or NULL (0)
+  int block_size;
+  int page_elems;             // nkv * bs * hd
+  int64_t num_blocks;
+  int* err_word;
+};
+
+__device__ __forceinline__ uint4 e4m3x8_to_bf16x8(const uint2 v) {
+  auto widen = [](uint32_t two) -> uint32_t {   // two e4m3 (low 16 bits) -> two bf16
+    uint32_t h;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"(static_cast<uint16_t>(two)));
+    float lo, hi;
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "cvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}"
+        : "=f"(lo), "=f"(hi)
+        : "r"(h));
+    return pack_bf16x2(lo, hi);
+  };
+  return make_uint4(widen(v.x), widen(v.x >> 16), widen(v.y), widen(v.y >> 16));
+}
+
+// grid (page slot, sequence); one CTA widens one page of K and of V.
+__global__ void __launch_bounds__(256) dequant_pages_kernel(const DequantPagesParams p) {
+  const int slot = blockIdx.x, seq = blockIdx.y;
+  const int len = p.cu_q[seq + 1] - p.cu_q[seq];
+  const int ctx = (p.q_start ? p.q_start[seq] : 0) + len;          // keys 0 .. ctx-1 are read
+  if (len <= 0 || slot >= (ctx + p.block_size - 1) / p.block_size) return;
+  int64_t blk = p.page_table[static_cast<int64_t>(seq) * p.page_table_stride + slot];
+  if (blk < 0 || blk >= p.num_blocks) {
+    if (threadIdx.x == 0) atomicExch(p.err_word, kDevBadIndex);
+    return;
+  }
+  const int64_t dst_page = static_cast<int64_t>(seq) * p.page_table_width + slot;
+  const int vecs = p.page_elems / 8;                               // 8 elements per thread step
+  const uint2* ks = reinterpret_cast<const uint2*>(p.k_src + blk * p.page_elems);
+  const uint2* vs = reinterpret_cast<const uint2*>(p.v_src + blk * p.page_elems);
+  uint4* kd = reinterpret_cast<uint4*>(p.k_dst + dst_page * p.page_elems);
+  uint4* vd = reinterpret_cast<uint4*>(p.v_dst + dst_page * p.page_elems);
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x) {
+    kd[i] = e4m3x8_to_bf16x8(__ldg(ks + i));
+    vd[i] = e4m3x8_to_bf16x8(__ldg(vs + i));
+  }
+}
+
 }  // namespace b200attn

@@ -56,13 +56,7 @@ constexpr float kPfRescaleThreshold = 8.f;  // log2 units
 #define B200ATTN_PF_POLY_EVERY 0
 #endif
 constexpr int kPfPolyEvery = B200ATTN_PF_POLY_EVERY;
-// Softmax weights as f16 pairs straight out of a packed ex2 (two exponentials per MUFU
-// instruction, no separate conversion), summed in f16 pairs over 8 keys at a time and then in
-// fp32.  P is then an f16 A operand of the PV MMA (V stays bf16).
-#ifndef B200ATTN_PF_F16_EXP
-#define B200ATTN_PF_F16_EXP 0
-#endif
-constexpr bool kPfF16Exp = B200ATTN_PF_F16_EXP != 0;
+
 constexpr int kPfSeqCache = 1024;           // sequences whose cu_q is cached in shared memory
 constexpr int kPfLevelOrderMaxSeqs = 64;    // above this, items keep plain sequence order
 constexpr int kPfItemTable = 128;           // rounds whose item is decoded once, up front
@@ -430,7 +424,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       // stay warp-uniform); lane 0 issues.
       const bool is_pv = warp == 3;
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfM, kPfN, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true, kPfF16Exp);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfM, HD, false, true);
       // high descriptor word: SBO = 1024 B, descriptor version 1, 128-byte swizzle
       constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t kLboV = (static_cast<uint32_t>(L::kSubBytes) >> 4) << 16;  // V: next 64 d
@@ -639,46 +633,25 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const float m_sub = (WIN && m_new == -INFINITY) ? 0.f : m_new;
         const uint64_t negm2 = pack_f32x2(-m_sub, -m_sub);
         uint64_t sum2[2] = {0ull, 0ull};
-        float sum_h = 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t preg[16];
-          if (kPfF16Exp) {
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8) {          // 8 keys: four pairs summed as f16 pairs
-              uint32_t acc = 0u;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int kx = q8 * 8 + i * 2;
-                const uint64_t x2 = fma_f32x2(
-                    pack_f32x2(__uint_as_float(sreg[c][kx]), __uint_as_float(sreg[c][kx + 1])),
-                    scale2, negm2);
-                float x0, x1;
-                unpack_f32x2(x2, x0, x1);
-                const uint32_t e = exp2_f16x2(x0, x1);
-                preg[kx >> 1] = e;
-                acc = i == 0 ? e : add_f16x2(acc, e);
-              }
-              sum_h += hsum_f16x2(acc);
+          for (int kx = 0; kx < 32; kx += 2) {
+            const uint64_t x2 = fma_f32x2(
+                pack_f32x2(__uint_as_float(sreg[c][kx]), __uint_as_float(sreg[c][kx + 1])), scale2,
+                negm2);
+            float x0, x1, e0, e1;
+            unpack_f32x2(x2, x0, x1);
+            if (kPfPolyEvery > 0 && ((kx >> 1) % (kPfPolyEvery > 0 ? kPfPolyEvery : 1)) ==
+                                        (kPfPolyEvery - 1)) {
+              exp2_poly_f32x2(x0, x1, e0, e1);
+            } else {
+              e0 = fast_exp2(x0);
+              e1 = fast_exp2(x1);
             }
-          } else {
-#pragma unroll
-            for (int kx = 0; kx < 32; kx += 2) {
-              const uint64_t x2 = fma_f32x2(
-                  pack_f32x2(__uint_as_float(sreg[c][kx]), __uint_as_float(sreg[c][kx + 1])), scale2,
-                  negm2);
-              float x0, x1, e0, e1;
-              unpack_f32x2(x2, x0, x1);
-              if (kPfPolyEvery > 0 && ((kx >> 1) % (kPfPolyEvery > 0 ? kPfPolyEvery : 1)) ==
-                                          (kPfPolyEvery - 1)) {
-                exp2_poly_f32x2(x0, x1, e0, e1);
-              } else {
-                e0 = fast_exp2(x0);
-                e1 = fast_exp2(x1);
-              }
-              sum2[(kx >> 1) & 1] = add_f32x2(sum2[(kx >> 1) & 1], pack_f32x2(e0, e1));
-              preg[kx >> 1] = pack_bf16x2(e0, e1);
-            }
+            sum2[(kx >> 1) & 1] = add_f32x2(sum2[(kx >> 1) & 1], pack_f32x2(e0, e1));
+            preg[kx >> 1] = pack_bf16x2(e0, e1);
           }
           tmem_st_32x16(s_addr + c * 16, preg);
         }
@@ -688,7 +661,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           unpack_f32x2(sum2[1], b0, b1);
           // this group's sum is relative to the max at ITS previous tile
           const float f = (m_last == -INFINITY) ? 0.f : fast_exp2(m_last - m_new);
-          l_run = l_run * f + ((a0 + a1) + (b0 + b1) + sum_h);
+          l_run = l_run * f + ((a0 + a1) + (b0 + b1));
           m_last = m_new;
         }
 #ifdef B200ATTN_PF_TRACE

@@ -213,30 +213,6 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
-// Two exponentials per MUFU instruction: round the pair to f16x2 and take ex2 on the packed
-// pair.  The result is the packed f16 pair itself (what the PV MMA wants as its A operand).
-// Inputs must stay below 16 (2^16 overflows f16); inputs below -25 give 0.
-__device__ __forceinline__ uint32_t exp2_f16x2(float x0, float x1) {
-  uint32_t h, e;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(e) : "r"(h));
-  return e;
-}
-__device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-// sum of the two halves of an f16x2 as fp32
-__device__ __forceinline__ float hsum_f16x2(uint32_t v) {
-  float lo, hi;
-  asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
-      "cvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}"
-      : "=f"(lo), "=f"(hi)
-      : "r"(v));
-  return lo + hi;
-}
-
 // 2^x for two values on the FMA and integer pipes (no MUFU).  x = n + f with n = round(x) taken
 // by the add-a-large-constant trick (n lands in the low mantissa bits of t), 2^f by a cubic
 // fitted on [-0.5, 0.5] (max relative error 1.0e-4), and n added to the exponent field.
@@ -379,11 +355,12 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
-// Instruction descriptor for kind::f16 with f32 accumulation; bf16 A/B (A may be f16 instead).
+// Instruction descriptor for kind::f16 with bf16 A/B and f32 accumulation.  (A and B must have
+// the same format: an f16 A with a bf16 B is refused by the hardware as an illegal instruction.)
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t m, uint32_t n, bool a_mn_major,
-                                                       bool b_mn_major, bool a_is_f16 = false) {
+                                                       bool b_mn_major) {
   return (1u << 4)                                  // D format f32
-         | ((a_is_f16 ? 0u : 1u) << 7)              // A format: 0 = f16, 1 = bf16
+         | (1u << 7)                                // A format bf16
          | (1u << 10)                               // B format bf16
          | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16)
          | ((n >> 3) << 17) | ((m >> 4) << 24);
