@@ -148,3 +148,60 @@ def test_paged_and_fresh_forms_agree_at_config2_shape(clean_error_word):
                             case.v.reshape(T, nkv, hd)[:, kh][None, None].float(), True,
                             case.scale)[0, 0]
         assert_attention_close(fresh[:, h], want, f"head {h}")
+
+
+@pytest.mark.parametrize("bs,hd", [(64, 128), (32, 64)])
+def test_non_finite_cache_slots_past_the_context_do_not_leak(bs, hd, clean_error_word):
+    """A live cache holds stale data in the slots of the last page that were never written, and
+    in pages listed beyond the context.  NaN / Inf there must not reach any output row (their
+    weights are zero, but 0 x NaN is NaN unless the rows are neutralised)."""
+    from b200attn import ops
+
+    g = torch.Generator().manual_seed(31 + bs)
+    nq, nkv = 8, 2
+    q_lens, starts = [70, 129, 200], [64, 0, 128]
+    nblks = [(s + t + bs - 1) // bs for s, t in zip(starts, q_lens)]
+    width = max(nblks) + 1
+    nb = sum(nblks) + 2
+    perm = torch.randperm(nb - 1, generator=g) + 1
+    pt = torch.zeros(len(q_lens), width, dtype=torch.int32)
+    o = 0
+    for i, n in enumerate(nblks):
+        pt[i, :n] = perm[o:o + n].int()
+        o += n
+    kc = randn_bf16((nb, nkv, bs, hd), g)
+    vc = randn_bf16((nb, nkv, bs, hd), g)
+    total = sum(q_lens)
+    q = randn_bf16((total, nq, hd), g)
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    wants = []
+    for i, (t, s) in enumerate(zip(q_lens, starts)):
+        qi = q[cu_q[i]:cu_q[i + 1]].transpose(0, 1)[None].float()
+        wants.append(restate.chunked_sdpa(qi, kc.float(), vc.float(), pt[i:i + 1, :nblks[i]], s,
+                                          hd ** -0.5)[0].transpose(0, 1))
+    # now poison everything past each context: the tail of the last page, and block 0 (which the
+    # unused page-table columns point at)
+    kc[0], vc[0] = float("nan"), float("inf")
+    for i, (t, s) in enumerate(zip(q_lens, starts)):
+        ctx = s + t
+        if ctx % bs:
+            blk = int(pt[i, ctx // bs])
+            kc[blk, :, ctx % bs:] = float("nan")
+            vc[blk, :, ctx % bs:] = float("-inf")
+    out = ops.prefill(q.cuda(), kc.cuda(), vc.cuda(), cu_q, scale=hd ** -0.5, page_table=pt.cuda(),
+                      q_start=torch.tensor(starts, dtype=torch.int32).cuda()).cpu()
+    for i in range(len(q_lens)):
+        assert_attention_close(out[cu_q[i]:cu_q[i + 1]], wants[i], f"seq {i}")
+
+
+def test_query_offsets_must_start_at_zero_and_stay_inside_q():
+    """Rows are addressed absolutely (cu_q[s] + row): offsets that start above 0 or end past the
+    query tensor are refused before anything is launched."""
+    from b200attn import _lib, ops
+
+    q = torch.zeros(64, 4, 64, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(64, 2, 64, dtype=torch.bfloat16, device="cuda")
+    for bad in ([32, 64], [0, 96]):
+        with pytest.raises(_lib.B200AttnError, match="bad argument"):
+            ops.prefill(q, k, k, torch.tensor(bad, dtype=torch.int32), scale=0.125)
+    assert ops.prefill(q, k, k, torch.tensor([0, 64], dtype=torch.int32), scale=0.125).shape == q.shape
