@@ -20,7 +20,9 @@ One JSON line is printed by rank 0.  Besides the contract keys it carries
   sustained     the same step replayed for about two seconds (median and spread),
   prefill       the config-2 causal prefill (tcgen05 kernel) in TFLOP/s against the tensor peak,
   extra_workloads  configs 1 and 3 (decode rows), and for N > 1 the row-parallel linear,
-  e2e_model     config 5: Llama-3.1-8B decode tokens/s through vLLM with this backend (TP = N).
+  e2e_model     config 5: Llama-3.1-8B decode tokens/s through vLLM with this backend (TP = N);
+                from N = 4 up also with the opt-in fused row-parallel linear
+                (e2e_model_fused_linear).
 `--impl reference` times the reference algorithm's CPU path (the oracle port; the Python
 reference tree itself is not present on the GPU machine) on a bounded sample per step.
 """
@@ -670,14 +672,15 @@ def run_rowlinear_bench(args):
         dist.destroy_process_group()
 
 
-def run_e2e_model_subprocess(args, rank: int, world: int, timeout_s: int = 600):
+def run_e2e_model_subprocess(args, rank: int, world: int, timeout_s: int = 600,
+                             port_offset: int = 23):
     """Config 5 (end-to-end Llama-3.1-8B decode through vLLM, `--workload c5`) as a child process
     of every rank, so that the engine gets a fresh CUDA context and its own process group.
     Returns rank 0's result line as a dict (None on the other ranks)."""
     env = dict(os.environ)
     if world > 1:
         # a rendezvous of its own: the parent's store keeps serving the parent's group
-        env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 23)
+        env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + port_offset)
         for k in ("TORCHELASTIC_USE_AGENT_STORE", "TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT",
                   "TORCHELASTIC_MAX_RESTARTS", "TORCHELASTIC_ERROR_FILE"):
             env.pop(k, None)
@@ -1003,13 +1006,20 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and "kv_dtype" not in wl:
         cpu = run_cpu_baseline(wl)
-    e2e_model = None
+    e2e_model = e2e_model_fused = None
     if not args.no_e2e_model and args.workload == "c4":
         # the engine gets the GPUs to itself: this process keeps only its CUDA context
         torch.cuda.empty_cache()
         barrier(world)
         e2e_model = run_e2e_model_subprocess(args, rank, world)
         barrier(world)
+        # from four ranks up, the same run with o_proj / down_proj through the fused GEMM +
+        # all-reduce launch (opt-in in the plugin), so the scaling record holds both
+        if world >= 4 and not args.fused_linear:
+            args.fused_linear = True
+            e2e_model_fused = run_e2e_model_subprocess(args, rank, world, port_offset=41)
+            args.fused_linear = False
+            barrier(world)
 
     if rank == 0:
         value = r["full_bytes"] / (r["ms_per_step"] * 1e-3) / 1e9
@@ -1064,6 +1074,8 @@ def main():
             line["extra_workloads"] = extras
         if e2e_model is not None:
             line["e2e_model"] = e2e_model
+        if e2e_model_fused is not None:
+            line["e2e_model_fused_linear"] = e2e_model_fused
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
