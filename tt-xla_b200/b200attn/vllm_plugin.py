@@ -13,6 +13,7 @@ math, the cache layout and the metadata derivation live there.
 """
 from __future__ import annotations
 
+import logging
 import os
 
 import torch
@@ -21,6 +22,8 @@ from vllm.v1.attention.backend import (AttentionBackend, AttentionCGSupport, Att
                                        AttentionMetadataBuilder, AttentionType)
 
 from . import backend as _b
+
+logger = logging.getLogger("b200attn")
 
 
 class B200VllmMetadataBuilder(AttentionMetadataBuilder[_b.B200Metadata]):
@@ -173,18 +176,26 @@ def create_group_communicator(group, device, max_n: int, max_tokens: int):
             "major": torch.cuda.get_device_capability(device)[0]}
     infos = [None] * dist.get_world_size(group)
     dist.all_gather_object(infos, mine, group=group)
-    ok, _why = ranks_allow_fused_row_parallel(infos, torch.cuda.can_device_access_peer)
+    ok, why = ranks_allow_fused_row_parallel(infos, torch.cuda.can_device_access_peer)
     comm = None
     if _agree(group, ok):
         try:
             comm = tp_linear.RowLinearComm(group, max_n=max_n, max_tokens=max_tokens,
                                            device=device)
-        except Exception:
+        except Exception as exc:
+            why = f"communicator creation failed: {exc}"
             comm = None
         if not _agree(group, comm is not None):
             if comm is not None:
                 comm.close()
             comm = None
+    elif ok:
+        why = "another rank refused"
+    if dist.get_rank(group) == 0:
+        if comm is not None:
+            logger.warning("b200attn: fused row-parallel linear ON for %d ranks", len(infos))
+        else:
+            logger.warning("b200attn: fused row-parallel linear stays off: %s", why)
     return comm
 
 
