@@ -16,6 +16,10 @@ import torch
 from . import _lib
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+# Scratch that was outgrown stays allocated: a CUDA graph captured earlier still launches into
+# it, and its arrival counters must stay zero (memory handed back to the allocator could be
+# given to another tensor).
+_retired_workspaces: list[torch.Tensor] = []
 
 
 CACHE_BF16, CACHE_FP8_E4M3 = 0, 1     # enum b200attn_cache_dtype
@@ -254,6 +258,8 @@ def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
     key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired_workspaces.append(ws)
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
@@ -462,6 +468,8 @@ def _widen_fp8_pages(k_cache, v_cache, page_table, cu_q, q_start, num_seqs):
     key = (dev.index or 0, torch.cuda.current_stream(dev).cuda_stream, nkv, bs, hd)
     have = _fp8_scratch.get(key)
     if have is None or have[0].shape[0] < pages:
+        if have is not None:
+            _retired_workspaces.extend(have[:2])
         grow = max(pages, 2 * have[0].shape[0] if have is not None else 0)
         have = (torch.empty((grow, nkv, bs, hd), dtype=torch.bfloat16, device=dev),
                 torch.empty((grow, nkv, bs, hd), dtype=torch.bfloat16, device=dev), {})
@@ -497,7 +505,7 @@ def read_error_word(device: Optional[torch.device] = None) -> int:
         )
     if word.value:
         # an aborted launch may have left arrival counters behind: start the scratch afresh
-        for ws in _workspaces.values():
+        for ws in list(_workspaces.values()) + _retired_workspaces:
             if ws.device == dev:
                 ws[:TICKET_BYTES].zero_()
     return int(word.value)

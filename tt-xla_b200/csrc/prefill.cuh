@@ -278,6 +278,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int group = warp >> 2;               // warpgroup = role
+#ifdef B200ATTN_PF_TRACE
+  const long long tr_entry = clock64();
+#endif
 
   // A CTA of this launch just gave up on a wait: do not repeat the timeout per CTA.
   if (timeout_drain_window(p.err_word)) return;
@@ -524,6 +527,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #ifdef B200ATTN_PF_TRACE
       tr_acc[7] = clock64() - tr_start;
       tr_acc[6] = t;
+      tr_acc[5] = tr_start - tr_entry;     // prologue: entry to the start of the role
 #endif
       PF_TRACE_FLUSH(is_pv ? 5 : 2)
     }
