@@ -131,3 +131,24 @@ def test_many_sequences_use_plain_item_order(clean_error_word):
         want = restate.sdpa(q[a:b].transpose(0, 1)[None].float(), k[a:b].transpose(0, 1)[None].float(),
                             v[a:b].transpose(0, 1)[None].float(), True, hd ** -0.5)[0].transpose(0, 1)
         assert_attention_close(out[a:b], want, f"seq {i}")
+
+
+def test_more_sequences_than_the_shared_memory_cache_holds(clean_error_word):
+    """Above 1024 sequences the prefill kernel reads the sequence offsets from global memory
+    instead of its shared-memory copy, and a CTA has more rounds than its item table holds."""
+    from b200attn import ops
+
+    g = torch.Generator().manual_seed(19)
+    nq, nkv, hd, S = 32, 2, 64, 1100      # 35200 items: 238 rounds per CTA, table holds 128
+    lens = torch.randint(1, 40, (S,), generator=g).tolist()
+    total = sum(lens)
+    q = randn_bf16((total, nq, hd), g)
+    k = randn_bf16((total, nkv, hd), g)
+    v = randn_bf16((total, nkv, hd), g)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    out = ops.prefill(q.cuda(), k.cuda(), v.cuda(), cu, scale=hd ** -0.5).cpu()
+    for i in (0, 1, 511, 1023, 1024, 1099):
+        a, b = int(cu[i]), int(cu[i + 1])
+        want = restate.sdpa(q[a:b].transpose(0, 1)[None].float(), k[a:b].transpose(0, 1)[None].float(),
+                            v[a:b].transpose(0, 1)[None].float(), True, hd ** -0.5)[0].transpose(0, 1)
+        assert_attention_close(out[a:b], want, f"seq {i}")
