@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstring>
 #include <initializer_list>
 #include <mutex>
@@ -24,6 +25,11 @@ static_assert(kDecTicketBytes == B200ATTN_DECODE_TICKET_BYTES, "header and kerne
 // Diagnostics block: code, pad, globaltimer stamp of the latest timeout (see ptx.cuh).
 __device__ __align__(16) int g_err_word[4] = {0, 0, 0, 0};
 
+// Work counters of the prefill kernel's dynamic item list: a launch uses word (tag % slots) and
+// claims it by its tag (see prefill_draw), so nothing has to be cleared between launches.
+__device__ unsigned long long g_pf_sched[kPfSchedSlots];
+static std::atomic<uint32_t> g_pf_launch_seq{0};
+
 // Split-KV scratch of b200attn_paged_decode_static.  In host code this name is only a handle
 // for cudaGetSymbolAddress; kernels get the device address looked up below.
 static __device__ __align__(256) unsigned char g_static_workspace[B200ATTN_STATIC_WORKSPACE_BYTES];
@@ -37,6 +43,7 @@ struct DeviceInfo {
   bool ready = false;
   int sm_count = 0;
   int* err_word = nullptr;
+  unsigned long long* pf_sched = nullptr;
 };
 
 static std::mutex g_mutex;
@@ -69,6 +76,11 @@ static int get_device(DeviceInfo** out) {
       return B200ATTN_ERR_NO_DEVICE;
     }
     d.err_word = static_cast<int*>(p);
+    if (cudaGetSymbolAddress(&p, g_pf_sched) != cudaSuccess) {
+      cudaGetLastError();
+      return B200ATTN_ERR_NO_DEVICE;
+    }
+    d.pf_sched = static_cast<unsigned long long*>(p);
     if (!g_encode) {
       void* fn = nullptr;
       cudaDriverEntryPointQueryResult q;
@@ -864,6 +876,10 @@ int b200attn_prefill_ex(void* out, int64_t out_row_stride, const void* q, int64_
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err_word = dev->err_word;
+  uint32_t tag = ++g_pf_launch_seq;
+  if (tag == 0) tag = ++g_pf_launch_seq;      // 0 marks a clear counter word
+  p.sched_tag = tag;
+  p.sched = dev->pf_sched + tag % kPfSchedSlots;
 #ifdef B200ATTN_PF_TRACE
   p.trace = g_pf_trace;
 #endif
@@ -945,6 +961,11 @@ int b200attn_read_error_word(int32_t* out_host, void* stream) {
   cudaError_t e = cudaMemcpyAsync(out_host, dev->err_word, sizeof(int), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaMemsetAsync(dev->err_word, 0, sizeof(int), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && *out_host != 0) {
+    // a launch that gave up may have left a prefill work counter half-way: clear them all
+    e = cudaMemsetAsync(dev->pf_sched, 0, sizeof(unsigned long long) * kPfSchedSlots, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  }
   return static_cast<int>(e);
 }
 

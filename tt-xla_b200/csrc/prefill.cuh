@@ -33,8 +33,13 @@
 //                 sums, reads O, hands it back, normalises by 1/l and stores bf16 rows.
 // Registers follow the roles (setmaxnreg): the two softmax warpgroups hold a whole S row each.
 // Items are ordered heaviest first (by the index of the 128-row block inside its sequence,
-// highest first, heads of one block adjacent) and dealt to the CTAs in rounds of alternating
-// direction (0..G-1, G-1..0, ...), which evens out the per-CTA sums of a sorted list.
+// highest first, heads of one block adjacent) and handed out dynamically: a CTA takes the next
+// item of the list from a global counter when it is about to need one (longest-processing-time
+// -first list scheduling, which also absorbs the run-to-run differences between CTAs that a
+// static deal cannot).  The counter needs no clearing launch: its word carries a tag that is
+// unique to the launch, a CTA that finds another tag claims the word for this launch with a
+// compare-and-swap, and the CTA that draws the last end marker puts the word back to zero (so
+// that a replay of a captured launch, which carries the same tag, starts afresh).
 // Every mbarrier wait is bounded; tensor memory is always freed before exit.
 #pragma once
 #include "ptx.cuh"
@@ -59,7 +64,9 @@ constexpr int kPfPolyEvery = B200ATTN_PF_POLY_EVERY;
 
 constexpr int kPfSeqCache = 1024;           // sequences whose cu_q is cached in shared memory
 constexpr int kPfLevelOrderMaxSeqs = 64;    // above this, items keep plain sequence order
-constexpr int kPfItemTable = 128;           // rounds whose item is decoded once, up front
+constexpr int kPfQueue = 16;                // items in flight inside a CTA (fetched .. epilogue)
+constexpr int kPfBlockTab = 1024;           // 128-row blocks whose place in the list is tabulated
+constexpr int kPfSchedSlots = 64;           // counter words; a launch uses word tag % 64
 // register budgets per warpgroup (sum = 4 x 128, the per-thread budget the kernel launches with)
 constexpr int kPfRegsProducer = 88;
 constexpr int kPfRegsSoftmax = 184;
@@ -83,6 +90,8 @@ struct PrefillParams {
   int64_t num_blocks;
   float scale_log2;
   int* err_word;
+  unsigned long long* sched;   // this launch's counter word: (tag << 32) | next item
+  uint32_t sched_tag;          // unique per launch on a device, never 0
 #ifdef B200ATTN_PF_TRACE
   unsigned long long* trace;   // [CTA][role 0..5][8] cycles spent per wait site (debug builds only)
 #endif
@@ -98,7 +107,17 @@ struct PrefillParams {
   if (lane == 0 && p.trace)                                                          \
     for (int i_ = 0; i_ < 8; ++i_)                                                   \
       p.trace[(static_cast<size_t>(blockIdx.x) * 6 + (role)) * 8 + i_] = tr_acc[i_];
+// timeline of one CTA: clock of event `ev` of KV tile `t` (counted over the CTA's items)
+#define PF_TL(ev, t)                                                                 \
+  if (p.trace && blockIdx.x == 5 && (t) < 160u && (threadIdx.x & 31) == 0)           \
+    p.trace[148 * 6 * 8 + (t) * 16 + (ev)] = clock64();
+// ... and of item-level event `ev` of the CTA's n-th item
+#define PF_TLI(ev, n)                                                                \
+  if (p.trace && blockIdx.x == 5 && (n) < 32u && (threadIdx.x & 31) == 0)            \
+    p.trace[148 * 6 * 8 + 160 * 16 + (n) * 8 + (ev)] = clock64();
 #else
+#define PF_TL(ev, t)
+#define PF_TLI(ev, n)
 #define PF_TRACE_DECL
 #define PF_TRACE_BEGIN()
 #define PF_TRACE_END(site)
@@ -117,13 +136,15 @@ struct PrefillSmem {
   static constexpr int kQOff = 0;                         // two Q buffers (by item parity)
   static constexpr int kRingOff = 2 * kTileBytes;
   static constexpr int kSeqOff = kRingOff + kSlots * kTileBytes;
-  static constexpr int kItemOff = kSeqOff + (kPfSeqCache + 4) * 4;   // keeps 16-byte alignment
-  static constexpr int kMaxOff = kItemOff + kPfItemTable * 16;       // running max [tile parity][row]
+  static constexpr int kPrefixOff = kSeqOff + (kPfSeqCache + 4) * 4;   // blocks before a sequence
+  static constexpr int kItemOff = kPrefixOff + (kPfSeqCache + 4) * 4;  // keeps 16-byte alignment
+  static constexpr int kTabOff = kItemOff + kPfQueue * 16;             // list position -> block
+  static constexpr int kMaxOff = kTabOff + kPfBlockTab * 4;            // running max [tile parity][row]
   static constexpr int kStatOff = kMaxOff + 2 * kPfM * 4;            // (max, sum) [item parity][group][row]
   static constexpr int kBarOff = kStatOff + 2 * 2 * kPfM * 8;
   // q_full[2] q_empty[2] k_full[kRing] v_full[kRing] k_empty[kRing] v_empty[kRing] s_full[3] p_full[3] pv_done[3] m_ready[2]
   // o_full o_empty stat_full[2] stat_empty[2]
-  static constexpr int kNumBars = 4 + 2 * kSlots + 17;
+  static constexpr int kNumBars = 4 + 2 * kSlots + 17 + kPfQueue;
   static constexpr int kTotalBytes = kBarOff + kNumBars * 8 + 16 + 1024;
   static_assert(kItemOff % 16 == 0, "16-byte vector access alignment");
   static_assert(kBarOff % 8 == 0, "barrier alignment");
@@ -149,18 +170,26 @@ struct PrefillItem {
 
 // Item index -> (sequence, 128-row block, head).  `cu` is cu_q (shared-memory copy when the
 // batch fits the cache).  Heaviest first: blocks ranked by their index inside their sequence,
-// highest first across sequences; the heads of one block are adjacent.  The search costs
-// microseconds, so the kernel runs it once per round up front (one thread per round) and the
-// roles read the result from shared memory.
+// highest first across sequences; the heads of one block are adjacent.  Batches of many
+// sequences keep plain sequence order (later blocks of a sequence first) and find the sequence
+// by bisection of `prefix` (128-row blocks before each sequence; NULL = scan).  For the
+// level order `prefix` holds the block COUNT of each sequence instead (NULL = compute).  One
+// thread of the CTA runs the search per item, one item ahead of the loads, and the roles read
+// the result from a shared-memory queue.
 __device__ __forceinline__ PrefillItemKey prefill_find_item(const PrefillParams& p,
-                                                           const int32_t* cu, int item) {
+                                                           const int32_t* cu,
+                                                           const int32_t* prefix, uint32_t item) {
   PrefillItemKey key{-1, 0, 0, 0};
-  if (item >= p.total_items) return key;
+  if (item >= static_cast<uint32_t>(p.total_items)) return key;
   key.head = item % p.num_q_heads;
   const int t = item / p.num_q_heads;
-  auto nblk = [&](int s) { return (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem; };
+  const bool level_order = p.num_seqs <= kPfLevelOrderMaxSeqs;
+  auto nblk = [&](int s) {
+    return (level_order && prefix) ? prefix[s]
+                                   : (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem;
+  };
   int seq = -1, blk = 0;
-  if (p.num_seqs <= kPfLevelOrderMaxSeqs) {
+  if (level_order) {
     int max_n = 0;
     for (int s = 0; s < p.num_seqs; ++s) max_n = max(max_n, nblk(s));
     auto at_or_above = [&](int r) {   // number of blocks whose index is >= r; decreasing in r
@@ -185,6 +214,15 @@ __device__ __forceinline__ PrefillItemKey prefill_find_item(const PrefillParams&
       }
     }
     blk = lo;
+  } else if (prefix) {
+    int lo = 0, hi = p.num_seqs - 1;   // last sequence whose first block is at or before t
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (prefix[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    seq = lo;
+    blk = nblk(lo) - 1 - (t - prefix[lo]);
+    if (blk < 0) return key;
   } else {
     int acc = 0;
     for (int s = 0; s < p.num_seqs; ++s) {
@@ -224,9 +262,30 @@ __device__ __forceinline__ bool prefill_expand_item(const PrefillParams& p,
   return it.n_tiles > 0;
 }
 
-// Item handled by CTA `cta` of `num_ctas` in round `round` (alternating direction per round).
-__device__ __forceinline__ int prefill_item_of(int round, int cta, int num_ctas) {
-  return round * num_ctas + ((round & 1) ? (num_ctas - 1 - cta) : cta);
+// Drawing the next index of the launch's item list is one atomicAdd on the launch's counter
+// word, issued well before its result is needed (prefill_draw_resolve).  Indices >= total are
+// end markers; every CTA draws exactly one, and the CTA that draws the last of them clears the
+// word.  An add that found another launch's tag in the word (the first draws of a launch) did
+// not count: the word is claimed for this launch and the draw repeated.
+__device__ __forceinline__ uint32_t prefill_draw_resolve(unsigned long long* word, uint32_t tag,
+                                                         uint32_t total, uint32_t num_ctas,
+                                                         unsigned long long drawn) {
+  for (int tries = 0; tries < 4096; ++tries) {
+    if (static_cast<uint32_t>(drawn >> 32) == tag) {
+      const uint32_t idx = static_cast<uint32_t>(drawn);
+      if (idx == total + num_ctas - 1u)
+        *reinterpret_cast<volatile unsigned long long*>(word) = 0ull;
+      return idx;
+    }
+    // Add again only once the word is this launch's: adds on a word that is still to be
+    // claimed would make every claim's compare fail.
+    const unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(word);
+    if (static_cast<uint32_t>(cur >> 32) == tag)
+      drawn = atomicAdd(word, 1ull);
+    else
+      atomicCAS(word, cur, static_cast<unsigned long long>(tag) << 32);
+  }
+  return 0xffffffffu;   // never seen; reads as an end marker
 }
 
 template <int N>
@@ -252,7 +311,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint8_t* q_smem = smem + L::kQOff;
   uint8_t* ring = smem + L::kRingOff;
   int32_t* cu_smem = reinterpret_cast<int32_t*>(smem + L::kSeqOff);
-  PrefillItemKey* item_table = reinterpret_cast<PrefillItemKey*>(smem + L::kItemOff);
+  int32_t* prefix_smem = reinterpret_cast<int32_t*>(smem + L::kPrefixOff);
+  PrefillItemKey* item_q = reinterpret_cast<PrefillItemKey*>(smem + L::kItemOff);
   float* m_sh = reinterpret_cast<float*>(smem + L::kMaxOff);          // [tile parity][row]
   float2* stat_sh = reinterpret_cast<float2*>(smem + L::kStatOff);    // [item parity][group][row]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -272,6 +332,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* o_empty = m_ready + 2;           // O of the item read out (epilogue -> PV issuer)
   uint64_t* stat_full = o_empty + 1;         // [2] both groups' (max, sum) written
   uint64_t* stat_empty = stat_full + 2;      // [2] ... and read by the epilogue
+  uint64_t* item_full = stat_empty + 2;      // [kPfQueue] the n-th item of this CTA is in the queue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -289,14 +350,48 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   if (cu_cached)
     for (int s = threadIdx.x; s <= p.num_seqs; s += blockDim.x) cu_smem[s] = p.cu_q[s];
   const int32_t* cu = cu_cached ? cu_smem : p.cu_q;
+  // For the item search: batches of many sequences get the number of 128-row blocks before
+  // each sequence, small batches (level order) the block count of each sequence.
+  const bool use_prefix = cu_cached && p.num_seqs > kPfLevelOrderMaxSeqs;
   if (cu_cached) __syncthreads();
-  const int num_rounds = (p.total_items + gridDim.x - 1) / gridDim.x;
-  for (int r = threadIdx.x; r < min(num_rounds, kPfItemTable); r += blockDim.x)
-    item_table[r] = prefill_find_item(p, cu, prefill_item_of(r, blockIdx.x, gridDim.x));
-  auto get_item = [&](int round, PrefillItem& it) {
-    const PrefillItemKey key =
-        round < kPfItemTable ? item_table[round]
-                             : prefill_find_item(p, cu, prefill_item_of(round, blockIdx.x, gridDim.x));
+  if (cu_cached && !use_prefix)
+    for (int s = threadIdx.x; s < p.num_seqs; s += blockDim.x)
+      prefix_smem[s] = (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem;
+  if (use_prefix && warp == 0) {
+    // each lane sums a run of consecutive sequences, a warp scan turns the run totals into offsets
+    const int per = (p.num_seqs + 31) / 32;
+    const int s0 = lane * per, s1 = min(p.num_seqs, s0 + per);
+    int run = 0;
+    for (int s = s0; s < s1; ++s) run += (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem;
+    int incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int acc = incl - run;
+    for (int s = s0; s < s1; ++s) {
+      prefix_smem[s] = acc;
+      acc += (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem;
+    }
+  }
+  // Small lists are tabulated once, all threads searching in parallel, so that taking an item
+  // costs the drawing thread one look-up instead of a search.
+  if (cu_cached && p.total_items / p.num_q_heads <= kPfBlockTab) {
+    __syncthreads();
+    const int total_blocks = p.total_items / p.num_q_heads;
+    uint32_t* blk_tab = reinterpret_cast<uint32_t*>(smem + L::kTabOff);   // (sequence << 16) | block
+    for (int b = threadIdx.x; b < total_blocks; b += blockDim.x) {
+      const PrefillItemKey key = prefill_find_item(p, cu, prefix_smem, b * p.num_q_heads);
+      blk_tab[b] = (static_cast<uint32_t>(key.seq) << 16) | static_cast<uint32_t>(key.q0 / kPfRowsPerItem);
+    }
+  }
+  // The n-th item of this CTA, for every role but the one that fetches it (the K producer):
+  // false at the end marker (and once a wait of this CTA has been abandoned).
+  auto take_item = [&](uint32_t n, PrefillItem& it) {
+    mbar_wait(&item_full[n % kPfQueue], (n / kPfQueue) & 1, abort_flag, p.err_word);
+    if (*abort_flag) return false;
+    const PrefillItemKey key = item_q[n % kPfQueue];
     return prefill_expand_item(p, key, cu, it);
   };
 
@@ -318,6 +413,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
     }
+    for (int i = 0; i < kPfQueue; ++i) mbar_init(&item_full[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -353,9 +449,45 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #ifdef B200ATTN_PF_TRACE
       const long long tr_start = clock64();
 #endif
-      for (int round = 0; round < num_rounds; ++round) {
+      // The K producer is the role that runs furthest ahead: its lane 0 draws the CTA's items
+      // from the launch's list and queues them for everybody.  The atomic that draws item n + 1
+      // is issued behind the first K tile of item n and its result is looked at once the last
+      // K tile of item n has been issued, so its latency stays off the loads' path.
+      bool more = !is_v && lane == 0;
+      unsigned long long drawn = 0;
+      const bool use_tab = cu_cached && p.total_items / p.num_q_heads <= kPfBlockTab;
+      const int32_t* prefix = cu_cached ? prefix_smem : nullptr;
+      const uint32_t* blk_tab = reinterpret_cast<const uint32_t*>(smem + L::kTabOff);
+      auto draw = [&]() {
+        if (more) drawn = atomicAdd(p.sched, 1ull);
+      };
+      auto publish = [&](uint32_t n) {
+        if (more) {
+          const uint32_t idx = prefill_draw_resolve(
+              p.sched, p.sched_tag, static_cast<uint32_t>(p.total_items), gridDim.x, drawn);
+          PrefillItemKey key{-1, 0, 0, 0};
+          if (idx < static_cast<uint32_t>(p.total_items)) {
+            if (use_tab) {
+              const uint32_t e = blk_tab[idx / p.num_q_heads];
+              key.seq = static_cast<int>(e >> 16);
+              key.q0 = static_cast<int>(e & 0xffffu) * kPfRowsPerItem;
+              key.head = idx % p.num_q_heads;
+              key.start = p.q_start ? p.q_start[key.seq] : 0;
+            } else {
+              key = prefill_find_item(p, cu, prefix, idx);
+            }
+          }
+          more = key.seq >= 0;
+          item_q[n % kPfQueue] = key;
+          mbar_arrive(&item_full[n % kPfQueue]);
+        }
+      };
+      draw();
+      publish(0);
+      for (uint32_t n = 0;; ++n) {
+        __syncwarp();
         PrefillItem it;
-        if (!get_item(round, it)) continue;
+        if (!take_item(n, it)) break;
         const int kvh = it.head / p.group;
         if (!is_v) {
           const int ip = item_n & 1;
@@ -384,6 +516,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             mbar_wait(&retired[u % 3u], (u / 3u) & 1, abort_flag, p.err_word);
             PF_TRACE_END(1);
           }
+          PF_TL(is_v ? 14 : 13, t)
           uint8_t* dst = my_ring + slot * L::kTileBytes;
           if (lane == 0) mbar_arrive_expect_tx(&full[slot], L::kTileBytes);
           if (p.kv_is_paged) {
@@ -414,7 +547,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               tma_load_2d(dst + s * L::kSubBytes, tm, &full[slot], kvh * HD + s * 64,
                           it.seq_q_begin + j * kPfN, pol_kv);
           }
+          if (i == 0) draw();
         }
+        publish(n + 1);
       }
 #ifdef B200ATTN_PF_TRACE
       tr_acc[7] = clock64() - tr_start;
@@ -441,15 +576,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       uint8_t* k_ring = ring;
       uint8_t* v_ring = ring + kRing * L::kTileBytes;
       uint32_t t = 0, item_no = 0;
-      for (int round = 0; round < num_rounds; ++round) {
+      for (;;) {
         PrefillItem it;
-        if (!get_item(round, it)) continue;
+        PF_TLI(is_pv ? 0 : 2, item_no)
+        if (!take_item(item_no, it)) break;
+        PF_TLI(is_pv ? 1 : 3, item_no)
         const int n = it.n_tiles;
         const int ip = item_no & 1;
         if (!is_pv) {
           PF_TRACE_BEGIN();
           mbar_wait(&q_full[ip], (item_no >> 1) & 1, abort_flag, p.err_word);
           PF_TRACE_END(0);
+          PF_TLI(4, item_no)
         }
         const uint32_t q_lo = (smem_u32(q_smem + ip * L::kTileBytes) >> 4) | kLboK;
         const int last_pos = it.first_pos + it.rows_valid - 1;
@@ -461,11 +599,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             PF_TRACE_BEGIN();
             mbar_wait(&k_full[slot], (t / kRing) & 1, abort_flag, p.err_word);
             PF_TRACE_END(1);
+            PF_TL(0, t)
             if (t >= 3) {     // S_b still holds P of tile t-3 until its PV has retired
               PF_TRACE_BEGIN();
               mbar_wait(&pv_done[b], ((t - 3) / 3u) & 1, abort_flag, p.err_word);
               PF_TRACE_END(2);
             }
+            PF_TL(1, t)
             tc_fence_after_sync();
             const uint32_t k_lo = (smem_u32(k_ring + slot * L::kTileBytes) >> 4) | kLboK;
             const uint32_t d = tmem_base + b * kPfN;
@@ -479,12 +619,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               // the last QK of the item has been issued: its Q buffer is free once it retires
               if (j == n - 1) umma_commit(&q_empty[ip]);
             }
+            PF_TL(2, t)
           } else {
             // ---- O (+)= P_t V_t
             uint8_t* vt = v_ring + slot * L::kTileBytes;
             PF_TRACE_BEGIN();
             mbar_wait(&v_full[slot], (t / kRing) & 1, abort_flag, p.err_word);
             PF_TRACE_END(1);
+            PF_TL(3, t)
             if (j == n - 1) {
               // Keys past the item's last query row are masked in P, but 0 x (stale, possibly
               // non-finite cache contents) would still poison the row: zero those V rows.
@@ -502,11 +644,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             PF_TRACE_BEGIN();
             mbar_wait(&p_full[b], (t / 3u) & 1, abort_flag, p.err_word);
             PF_TRACE_END(3);
+            PF_TL(4, t)
             if (j == 0) {   // O of the item before must have been read out before it is overwritten
               PF_TRACE_BEGIN();
               mbar_wait(o_empty, (item_no & 1) ^ 1, abort_flag, p.err_word);
               PF_TRACE_END(4);
             }
+            PF_TL(5, t)
             tc_fence_after_sync();
             const uint32_t p_tmem = tmem_base + b * kPfN;   // P over the first 64 columns of S_b
             const uint32_t v_lo = (smem_u32(vt) >> 4) | kLboV;
@@ -520,6 +664,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               }
               umma_commit(&pv_done[b]);
             }
+            PF_TL(6, t)
           }
         }
         ++item_no;
@@ -545,9 +690,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #ifdef B200ATTN_PF_TRACE
     const long long tr_start = clock64();
 #endif
-    for (int round = 0; round < num_rounds; ++round) {
+    for (;;) {
       PrefillItem it;
-      if (!get_item(round, it)) continue;
+      if (!take_item(item_no, it)) break;
       const int ip = item_no & 1;
       const int q_pos = it.first_pos + row;
       float l_run = 0.f, m_last = -INFINITY;   // this group's row sum, relative to m_last
@@ -562,6 +707,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         PF_TRACE_END(0);
 #ifdef B200ATTN_PF_TRACE
         const long long tr_tile = clock64();
+        if ((warp & 3) == 0) { PF_TL(7, t) }
 #endif
         tc_fence_after_sync();
 #ifdef B200ATTN_PF_NOSOFTMAX
@@ -578,16 +724,36 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #ifdef B200ATTN_PF_TRACE
         const long long tr_ld = clock64();
         tr_acc[3] += tr_ld - tr_tile;
+        if ((warp & 3) == 0) { PF_TL(8, t) }
 #endif
 
         const int key0 = j * kPfN;
+#ifdef B200ATTN_PF_MASK_ALWAYS
+        {
+          const bool dg = key0 + kPfN - 1 > it.first_pos;
+          const int lim = dg ? q_pos - key0 : 1000;
+          const int lim_w = dg ? it.first_pos + (warp & 3) * 32 - key0 : ((warp & 3) - 4) * 32;
+#else
         if (key0 + kPfN - 1 > it.first_pos) {   // tile crosses the diagonal for some row
+          const int lim = q_pos - key0;                                // the row sees keys 0 .. lim
+          const int lim_w = it.first_pos + (warp & 3) * 32 - key0;     // ... of the warp's first row
+#endif
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 4; ++c) {
+            if (lim_w < c * 32 + 31) {    // warp-uniform: some row of the warp loses a key of this chunk
 #pragma unroll
-            for (int kx = 0; kx < 32; ++kx)
-              if (key0 + c * 32 + kx > q_pos) sreg[c][kx] = 0xff800000u;   // -inf
+              for (int kx = 0; kx < 32; ++kx)
+                asm("{\n\t.reg .pred p;\n\t"
+                    "setp.lt.s32 p, %1, %2;\n\t"
+                    "selp.b32 %0, 0xff800000, %0, p;\n\t}"       // -inf
+                    : "+r"(sreg[c][kx])
+                    : "r"(lim), "r"(c * 32 + kx));
+            }
+          }
         }
+#ifdef B200ATTN_PF_TRACE
+        if ((warp & 3) == 0) { PF_TL(15, t) }
+#endif
         if (WIN && key0 < it.first_pos + kPfM - p.window) {   // below some row's window
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -610,6 +776,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #ifdef B200ATTN_PF_TRACE
         const long long tr_mx = clock64();
         tr_acc[4] += tr_mx - tr_ld;
+        if ((warp & 3) == 0) { PF_TL(9, t) }
 #endif
         // running max after the tile before (the other group publishes it as soon as it has it)
         float m_prev = -INFINITY;
@@ -633,6 +800,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         // it, so the S / P columns are quiescent.
 #ifdef B200ATTN_PF_TRACE
         const long long tr_ex = clock64();
+        if ((warp & 3) == 0) { PF_TL(10, t) }
 #endif
         const float m_sub = (WIN && m_new == -INFINITY) ? 0.f : m_new;
         const uint64_t negm2 = pack_f32x2(-m_sub, -m_sub);
@@ -671,6 +839,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #ifdef B200ATTN_PF_TRACE
         const long long tr_ex1 = clock64();
         tr_acc[5] += tr_ex1 - tr_ex;
+        if ((warp & 3) == 0) { PF_TL(11, t) }
 #endif
         // O row rescale (rare: only when the running max moved by more than the threshold):
         // every PV up to the tile before must have retired; PV of this tile waits for p_full.
@@ -701,6 +870,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         mbar_arrive(&p_full[b]);
 #ifdef B200ATTN_PF_TRACE
         tr_acc[6] += clock64() - tr_ex1;
+        if ((warp & 3) == 0) { PF_TL(12, t) }
 #endif
       }
       // ---- item end: hand this group's (max, sum) of the row to the epilogue
@@ -727,9 +897,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #ifdef B200ATTN_PF_TRACE
     const long long tr_start = clock64();
 #endif
-    for (int round = 0; round < num_rounds; ++round) {
+    for (;;) {
       PrefillItem it;
-      if (!get_item(round, it)) continue;
+      if (!take_item(item_no, it)) break;
       const int ip = item_no & 1;
       const uint32_t ph = (item_no >> 1) & 1;
       t_end += it.n_tiles;
@@ -737,6 +907,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       PF_TRACE_BEGIN();
       mbar_wait(&stat_full[ip], ph, abort_flag, p.err_word);
       PF_TRACE_END(0);
+      if ((warp & 3) == 0) { PF_TLI(5, item_no) }
       const float2 s0 = stat_sh[(ip * 2 + 0) * kPfM + row];
       const float2 s1 = stat_sh[(ip * 2 + 1) * kPfM + row];
       mbar_arrive(&stat_empty[ip]);
@@ -750,6 +921,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       PF_TRACE_END(1);
 #ifdef B200ATTN_PF_TRACE
       const long long tr_ep = clock64();
+      if ((warp & 3) == 0) { PF_TLI(6, item_no) }
 #endif
       tc_fence_after_sync();
       __nv_bfloat16* orow =
@@ -766,6 +938,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           mbar_arrive(o_empty);
 #ifdef B200ATTN_PF_TRACE
           tr_acc[2] += clock64() - tr_ep;
+          if ((warp & 3) == 0) { PF_TLI(7, item_no) }
 #endif
         }
         uint32_t packed[8];
