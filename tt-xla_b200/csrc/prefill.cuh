@@ -138,7 +138,7 @@ struct PrefillSmem {
   static constexpr int kSeqOff = kRingOff + kSlots * kTileBytes;
   static constexpr int kPrefixOff = kSeqOff + (kPfSeqCache + 4) * 4;   // blocks before a sequence
   static constexpr int kItemOff = kPrefixOff + (kPfSeqCache + 4) * 4;  // keeps 16-byte alignment
-  static constexpr int kTabOff = kItemOff + kPfQueue * 16;             // list position -> block
+  static constexpr int kTabOff = kItemOff + kPfQueue * 48;             // list position -> block
   static constexpr int kMaxOff = kTabOff + kPfBlockTab * 4;            // running max [tile parity][row]
   static constexpr int kStatOff = kMaxOff + 2 * kPfM * 4;            // (max, sum) [item parity][group][row]
   static constexpr int kBarOff = kStatOff + 2 * 2 * kPfM * 8;
@@ -151,7 +151,7 @@ struct PrefillSmem {
   static_assert(kTotalBytes <= 232448, "shared memory budget");
 };
 
-// Compact result of the item-order search (one per round, kept in shared memory).
+// Compact result of the item-order search.
 struct PrefillItemKey {
   int seq;    // -1 = no such item
   int q0;
@@ -160,13 +160,15 @@ struct PrefillItemKey {
 };
 
 // What every role needs to know about one work item.
-struct PrefillItem {
-  int seq, head, q0, seq_q_begin, seq_len_q, start;
+struct alignas(16) PrefillItem {
+  int seq, head, q0, seq_q_begin, seq_len_q, start;   // seq < 0: end of the CTA's work
   int rows_valid;     // query rows of the item that exist (the last block of a sequence is ragged)
   int first_pos;      // absolute position of the item's first query row
   int j0;             // first KV tile any row attends (0 without a sliding window)
   int n_tiles;        // KV tiles j0 .. j0 + n_tiles - 1
+  int pad[2];
 };
+static_assert(sizeof(PrefillItem) == 48, "queue entries are copied as three 16-byte vectors");
 
 // Item index -> (sequence, 128-row block, head).  `cu` is cu_q (shared-memory copy when the
 // batch fits the cache).  Heaviest first: blocks ranked by their index inside their sequence,
@@ -312,7 +314,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint8_t* ring = smem + L::kRingOff;
   int32_t* cu_smem = reinterpret_cast<int32_t*>(smem + L::kSeqOff);
   int32_t* prefix_smem = reinterpret_cast<int32_t*>(smem + L::kPrefixOff);
-  PrefillItemKey* item_q = reinterpret_cast<PrefillItemKey*>(smem + L::kItemOff);
+  PrefillItem* item_q = reinterpret_cast<PrefillItem*>(smem + L::kItemOff);
   float* m_sh = reinterpret_cast<float*>(smem + L::kMaxOff);          // [tile parity][row]
   float2* stat_sh = reinterpret_cast<float2*>(smem + L::kStatOff);    // [item parity][group][row]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -386,13 +388,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       blk_tab[b] = (static_cast<uint32_t>(key.seq) << 16) | static_cast<uint32_t>(key.q0 / kPfRowsPerItem);
     }
   }
-  // The n-th item of this CTA, for every role but the one that fetches it (the K producer):
-  // false at the end marker (and once a wait of this CTA has been abandoned).
+  // The n-th item of this CTA: false at the end marker (and once a wait of this CTA has been
+  // abandoned).  The K producer's lane 0 wrote the entry, fully expanded, so that taking it is a
+  // wait and three vector loads for everybody else.
   auto take_item = [&](uint32_t n, PrefillItem& it) {
     mbar_wait(&item_full[n % kPfQueue], (n / kPfQueue) & 1, abort_flag, p.err_word);
     if (*abort_flag) return false;
-    const PrefillItemKey key = item_q[n % kPfQueue];
-    return prefill_expand_item(p, key, cu, it);
+    const uint4* src = reinterpret_cast<const uint4*>(&item_q[n % kPfQueue]);
+    uint4* dst = reinterpret_cast<uint4*>(&it);
+    dst[0] = src[0];
+    dst[1] = src[1];
+    dst[2] = src[2];
+    return it.seq >= 0;
   };
 
   if (threadIdx.x == 0) {
@@ -477,8 +484,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               key = prefill_find_item(p, cu, prefix, idx);
             }
           }
-          more = key.seq >= 0;
-          item_q[n % kPfQueue] = key;
+          PrefillItem full;
+          if (!prefill_expand_item(p, key, cu, full)) full.seq = -1;
+          more = full.seq >= 0;
+          item_q[n % kPfQueue] = full;
           mbar_arrive(&item_full[n % kPfQueue]);
         }
       };
