@@ -150,6 +150,69 @@ def test_paged_and_fresh_forms_agree_at_config2_shape(clean_error_word):
         assert_attention_close(fresh[:, h], want, f"head {h}")
 
 
+def _fresh_inputs(users, T, nq, nkv, hd, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    mk = lambda h: torch.randn(users * T, h, hd, generator=g, device="cuda").bfloat16()
+    return mk(nq), mk(nkv), mk(nkv)
+
+
+def test_a_captured_launch_replays_with_a_fresh_item_counter(clean_error_word):
+    """The CTAs draw their work items from a counter word that carries the launch's tag; a CUDA
+    graph replays the launch with the SAME tag, so the word has to be back at zero after every
+    run.  Replays on new inputs must give the bits of an eager call on those inputs."""
+    from b200attn import ops
+
+    users, T, nq, nkv, hd = 3, 640, 8, 2, 128
+    cu_host = cu(users, T)
+    cu_dev = cu_host.cuda()
+    q, k, v = _fresh_inputs(users, T, nq, nkv, hd, 1)
+    out = torch.empty_like(q)
+    ops.prefill(q, k, v, cu_host, scale=hd ** -0.5, out=out, cu_q=cu_dev)      # warm-up, eager
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            ops.prefill(q, k, v, cu_host, scale=hd ** -0.5, out=out, cu_q=cu_dev)
+    torch.cuda.current_stream().wait_stream(side)
+    for seed in (2, 3, 4, 5):
+        q2, k2, v2 = _fresh_inputs(users, T, nq, nkv, hd, seed)
+        want = ops.prefill(q2, k2, v2, cu_host, scale=hd ** -0.5, cu_q=cu_dev)
+        q.copy_(q2), k.copy_(k2), v.copy_(v2)
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), f"replay with seed {seed}"
+    assert ops.read_error_word() == 0
+
+
+def test_launches_on_two_streams_keep_their_item_lists_apart(clean_error_word):
+    """Two prefill launches in flight at once (one per stream) draw from different counter
+    words; each must cover all of its own items."""
+    from b200attn import ops
+
+    users, T, nq, nkv, hd = 4, 1024, 16, 4, 128
+    cu_host = cu(users, T)
+    cu_dev = cu_host.cuda()
+    a = _fresh_inputs(users, T, nq, nkv, hd, 11)
+    b = _fresh_inputs(users, T, nq, nkv, hd, 12)
+    want_a = ops.prefill(*a, cu_host, scale=hd ** -0.5, cu_q=cu_dev)
+    want_b = ops.prefill(*b, cu_host, scale=hd ** -0.5, cu_q=cu_dev)
+    out_a, out_b = torch.empty_like(want_a), torch.empty_like(want_b)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    for _ in range(8):
+        out_a.zero_(), out_b.zero_()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s1):
+            ops.prefill(*a, cu_host, scale=hd ** -0.5, out=out_a, cu_q=cu_dev)
+        with torch.cuda.stream(s2):
+            ops.prefill(*b, cu_host, scale=hd ** -0.5, out=out_b, cu_q=cu_dev)
+        torch.cuda.synchronize()
+        assert torch.equal(out_a, want_a) and torch.equal(out_b, want_b)
+    assert ops.read_error_word() == 0
+
+
 @pytest.mark.parametrize("bs,hd", [(64, 128), (32, 64)])
 def test_non_finite_cache_slots_past_the_context_do_not_leak(bs, hd, clean_error_word):
     """A live cache holds stale data in the slots of the last page that were never written, and

@@ -36,8 +36,9 @@
 // highest first, heads of one block adjacent) and handed out dynamically: a CTA takes the next
 // item of the list from a global counter when it is about to need one (longest-processing-time
 // -first list scheduling, which also absorbs the run-to-run differences between CTAs that a
-// static deal cannot).  The counter needs no clearing launch: its word carries a tag that is
-// unique to the launch, a CTA that finds another tag claims the word for this launch with a
+// static deal cannot); its first item is the one with its own index, so no atomic stands before
+// the first loads.  The counter needs no clearing launch: its word carries a tag that is unique
+// to the launch, a CTA that finds another tag claims the word for this launch with a
 // compare-and-swap, and the CTA that draws the last end marker puts the word back to zero (so
 // that a replay of a captured launch, which carries the same tag, starts afresh).
 // Every mbarrier wait is bounded; tensor memory is always freed before exit.
@@ -264,11 +265,19 @@ __device__ __forceinline__ bool prefill_expand_item(const PrefillParams& p,
   return it.n_tiles > 0;
 }
 
-// Drawing the next index of the launch's item list is one atomicAdd on the launch's counter
-// word, issued well before its result is needed (prefill_draw_resolve).  Indices >= total are
-// end markers; every CTA draws exactly one, and the CTA that draws the last of them clears the
-// word.  An add that found another launch's tag in the word (the first draws of a launch) did
-// not count: the word is claimed for this launch and the draw repeated.
+// The launch's counter word is (tag << 32) | next list position.  CTA b starts with item b, so
+// a freshly claimed word stands at num_ctas (prefill_claim, early in every CTA's prologue).
+// Drawing the next position is one atomicAdd, issued well before its result is needed
+// (prefill_draw_resolve).  Positions >= total are end markers; every CTA that had a first item
+// draws exactly one, and the CTA that draws the last of them (position total + num_ctas - 1)
+// clears the word.  An add that found another launch's tag in the word did not count: the
+// word is claimed and the draw repeated.
+__device__ __forceinline__ void prefill_claim(unsigned long long* word, uint32_t tag,
+                                              uint32_t num_ctas) {
+  const unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(word);
+  if (static_cast<uint32_t>(cur >> 32) != tag)
+    atomicCAS(word, cur, (static_cast<unsigned long long>(tag) << 32) | num_ctas);
+}
 __device__ __forceinline__ uint32_t prefill_draw_resolve(unsigned long long* word, uint32_t tag,
                                                          uint32_t total, uint32_t num_ctas,
                                                          unsigned long long drawn) {
@@ -285,7 +294,7 @@ __device__ __forceinline__ uint32_t prefill_draw_resolve(unsigned long long* wor
     if (static_cast<uint32_t>(cur >> 32) == tag)
       drawn = atomicAdd(word, 1ull);
     else
-      atomicCAS(word, cur, static_cast<unsigned long long>(tag) << 32);
+      atomicCAS(word, cur, (static_cast<unsigned long long>(tag) << 32) | num_ctas);
   }
   return 0xffffffffu;   // never seen; reads as an end marker
 }
@@ -347,6 +356,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 
   // A CTA of this launch just gave up on a wait: do not repeat the timeout per CTA.
   if (timeout_drain_window(p.err_word)) return;
+  if (threadIdx.x == 96) prefill_claim(p.sched, p.sched_tag, gridDim.x);
 
   const bool cu_cached = p.num_seqs <= kPfSeqCache;
   if (cu_cached)
@@ -377,15 +387,35 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       acc += (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem;
     }
   }
-  // Small lists are tabulated once, all threads searching in parallel, so that taking an item
-  // costs the drawing thread one look-up instead of a search.
+  // Small lists are tabulated once (list position -> sequence, block), so that taking an item
+  // costs the drawing thread one look-up instead of a search.  Every (sequence, block) pair
+  // computes its own position: in the level order, the blocks with a higher index plus the
+  // earlier sequences that have a block of this index; in sequence order, the blocks of the
+  // sequences before plus the later blocks of its own.
   if (cu_cached && p.total_items / p.num_q_heads <= kPfBlockTab) {
     __syncthreads();
-    const int total_blocks = p.total_items / p.num_q_heads;
     uint32_t* blk_tab = reinterpret_cast<uint32_t*>(smem + L::kTabOff);   // (sequence << 16) | block
-    for (int b = threadIdx.x; b < total_blocks; b += blockDim.x) {
-      const PrefillItemKey key = prefill_find_item(p, cu, prefix_smem, b * p.num_q_heads);
-      blk_tab[b] = (static_cast<uint32_t>(key.seq) << 16) | static_cast<uint32_t>(key.q0 / kPfRowsPerItem);
+    const int S = p.num_seqs;
+    if (!use_prefix) {
+      const int lanes_per_seq = static_cast<int>(blockDim.x) / S;    // S <= 64 < blockDim.x
+      const int s_mine = static_cast<int>(threadIdx.x) % S;
+      if (static_cast<int>(threadIdx.x) < S * lanes_per_seq) {
+        const int n_mine = prefix_smem[s_mine];
+        for (int r = static_cast<int>(threadIdx.x) / S; r < n_mine; r += lanes_per_seq) {
+          int pos = 0;
+          for (int s2 = 0; s2 < S; ++s2) {
+            const int n2 = prefix_smem[s2];
+            pos += max(0, n2 - 1 - r) + ((s2 < s_mine && n2 > r) ? 1 : 0);
+          }
+          blk_tab[pos] = (static_cast<uint32_t>(s_mine) << 16) | static_cast<uint32_t>(r);
+        }
+      }
+    } else {
+      for (int s2 = threadIdx.x; s2 < S; s2 += blockDim.x) {
+        const int n2 = (cu[s2 + 1] - cu[s2] + kPfRowsPerItem - 1) / kPfRowsPerItem;
+        for (int r = 0; r < n2; ++r)
+          blk_tab[prefix_smem[s2] + n2 - 1 - r] = (static_cast<uint32_t>(s2) << 16) | static_cast<uint32_t>(r);
+      }
     }
   }
   // The n-th item of this CTA: false at the end marker (and once a wait of this CTA has been
@@ -458,8 +488,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #endif
       // The K producer is the role that runs furthest ahead: its lane 0 draws the CTA's items
       // from the launch's list and queues them for everybody.  The atomic that draws item n + 1
-      // is issued behind the first K tile of item n and its result is looked at once the last
-      // K tile of item n has been issued, so its latency stays off the loads' path.
+      // is issued behind the second-to-last K tile of item n and its result is looked at once
+      // the last K tile of item n has been issued, so its latency stays off the loads' path.
       bool more = !is_v && lane == 0;
       unsigned long long drawn = 0;
       const bool use_tab = cu_cached && p.total_items / p.num_q_heads <= kPfBlockTab;
@@ -470,8 +500,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       };
       auto publish = [&](uint32_t n) {
         if (more) {
-          const uint32_t idx = prefill_draw_resolve(
-              p.sched, p.sched_tag, static_cast<uint32_t>(p.total_items), gridDim.x, drawn);
+          // the first item of a CTA is the one with its own index: the list is drawn from
+          // position gridDim.x on, and no atomic stands before the first loads
+          const uint32_t idx =
+              n == 0 ? blockIdx.x
+                     : prefill_draw_resolve(p.sched, p.sched_tag,
+                                            static_cast<uint32_t>(p.total_items), gridDim.x, drawn);
           PrefillItemKey key{-1, 0, 0, 0};
           if (idx < static_cast<uint32_t>(p.total_items)) {
             if (use_tab) {
@@ -491,7 +525,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           mbar_arrive(&item_full[n % kPfQueue]);
         }
       };
-      draw();
       publish(0);
       for (uint32_t n = 0;; ++n) {
         __syncwarp();
@@ -556,7 +589,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               tma_load_2d(dst + s * L::kSubBytes, tm, &full[slot], kvh * HD + s * 64,
                           it.seq_q_begin + j * kPfN, pol_kv);
           }
-          if (i == 0) draw();
+          // late, so that the CTA commits to its next item when it is about to need it (a
+          // draw at the start of a long item would hand this CTA work that an idle one should
+          // take), but a tile before the result is looked at
+          if (i == max(0, it.n_tiles - 2)) draw();
         }
         publish(n + 1);
       }
