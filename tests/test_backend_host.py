@@ -178,3 +178,16 @@ def test_layer_wrapper_input_rules():
     assert layer.impl.num_kv_heads == 2 and layer.impl.sliding_window == 128
     with pytest.raises(TypeError, match="unexpected arguments"):
         backend.B200Attention(8, 64, 0.125, bogus=1)
+
+
+def test_split_count_env_override(monkeypatch):
+    """`B200ATTN_NUM_SPLITS` pins the split count of calls that leave it to the library."""
+    from b200attn import ops
+
+    monkeypatch.delenv("B200ATTN_NUM_SPLITS", raising=False)
+    assert ops._env_num_splits() == 0
+    monkeypatch.setenv("B200ATTN_NUM_SPLITS", "6")
+    assert ops._env_num_splits() == 6
+    monkeypatch.setenv("B200ATTN_NUM_SPLITS", "1000")
+    with pytest.raises(ValueError):
+        ops._env_num_splits()

@@ -18,12 +18,17 @@ Two metadata forms reach `forward`:
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
 import torch
 
 from . import ops
+
+# B200ATTN_NVTX=1 wraps every layer's forward in an NVTX range (timeline tools group the
+# launches of a layer under it); off, the path takes one global read more.
+_NVTX = os.environ.get("B200ATTN_NVTX", "0") not in ("", "0")
 
 # head_size must be a multiple of 32 on the reference device; page accounting keeps that
 # padding rule (attention.py:37-38, 721-771).
@@ -467,6 +472,12 @@ class B200AttentionBackendImpl:
         assert output is not None, "B200 attention requires an output buffer."
         if output_scale is not None or output_block_scale is not None:
             raise NotImplementedError("fused output quantisation is not supported")
+        if _NVTX:
+            with torch.cuda.nvtx.range(f"b200attn.forward[{getattr(layer, 'layer_name', '')}]"):
+                return self._forward(query, key, value, kv_cache, attn_metadata, output)
+        return self._forward(query, key, value, kv_cache, attn_metadata, output)
+
+    def _forward(self, query, key, value, kv_cache, attn_metadata, output):
         kv_pair = self._split_kv_cache(kv_cache)
         written, self.kv_written_upstream = self.kv_written_upstream, False
         if attn_metadata.is_varlen:

@@ -9,6 +9,7 @@ to.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -28,6 +29,19 @@ TICKET_BYTES = 65536                  # B200ATTN_DECODE_TICKET_BYTES
 
 def _cache_dtype(cache: torch.Tensor) -> int:
     return CACHE_FP8_E4M3 if cache.dtype == torch.float8_e4m3fn else CACHE_BF16
+
+
+def _env_num_splits() -> int:
+    """`B200ATTN_NUM_SPLITS=n` pins the split count of every decode call that leaves it to the
+    library (for sweeps and for ruling the cost model out while debugging); unset or 0 = the
+    model's choice.  Read on every call: changing it between steps is allowed outside graphs."""
+    raw = os.environ.get("B200ATTN_NUM_SPLITS", "")
+    if not raw:
+        return 0
+    n = int(raw)
+    if not 0 <= n <= 256:
+        raise ValueError(f"B200ATTN_NUM_SPLITS must be 0..256, got {raw!r}")
+    return n
 
 
 def _stream(t: torch.Tensor) -> int:
@@ -325,6 +339,8 @@ def paged_decode(
         _need_cuda(sinks)
         if sinks.dtype != torch.float32 or sinks.numel() != nq or not sinks.is_contiguous():
             raise ValueError("sinks must be a dense float32 tensor with one entry per q head")
+    if num_splits == 0:
+        num_splits = _env_num_splits()
     if num_splits == 0:
         ctx = max_context_len if max_context_len > 0 else page_table.shape[1] * bs
         if sliding_window > 0:
