@@ -773,16 +773,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #endif
 
         const int key0 = j * kPfN;
-#ifdef B200ATTN_PF_MASK_ALWAYS
-        {
-          const bool dg = key0 + kPfN - 1 > it.first_pos;
-          const int lim = dg ? q_pos - key0 : 1000;
-          const int lim_w = dg ? it.first_pos + (warp & 3) * 32 - key0 : ((warp & 3) - 4) * 32;
-#else
         if (key0 + kPfN - 1 > it.first_pos) {   // tile crosses the diagonal for some row
           const int lim = q_pos - key0;                                // the row sees keys 0 .. lim
           const int lim_w = it.first_pos + (warp & 3) * 32 - key0;     // ... of the warp's first row
-#endif
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             if (lim_w < c * 32 + 31) {    // warp-uniform: some row of the warp loses a key of this chunk
