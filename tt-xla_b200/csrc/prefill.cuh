@@ -171,77 +171,27 @@ struct alignas(16) PrefillItem {
 };
 static_assert(sizeof(PrefillItem) == 48, "queue entries are copied as three 16-byte vectors");
 
-// Item index -> (sequence, 128-row block, head).  `cu` is cu_q (shared-memory copy when the
-// batch fits the cache).  Heaviest first: blocks ranked by their index inside their sequence,
-// highest first across sequences; the heads of one block are adjacent.  Batches of many
-// sequences keep plain sequence order (later blocks of a sequence first) and find the sequence
-// by bisection of `prefix` (128-row blocks before each sequence; NULL = scan).  For the
-// level order `prefix` holds the block COUNT of each sequence instead (NULL = compute).  One
-// thread of the CTA runs the search per item, one item ahead of the loads, and the roles read
-// the result from a shared-memory queue.
+// List position -> (sequence, 128-row block, head) for lists too long to tabulate (more than
+// kPfBlockTab blocks or kPfSeqCache sequences): plain sequence order, later blocks of a
+// sequence first, found by a scan of cu_q.  Tabulated lists (the common case) are ordered
+// heaviest first, see the table build in the kernel's prologue.
 __device__ __forceinline__ PrefillItemKey prefill_find_item(const PrefillParams& p,
-                                                           const int32_t* cu,
-                                                           const int32_t* prefix, uint32_t item) {
+                                                           const int32_t* cu, uint32_t item) {
   PrefillItemKey key{-1, 0, 0, 0};
   if (item >= static_cast<uint32_t>(p.total_items)) return key;
   key.head = item % p.num_q_heads;
   const int t = item / p.num_q_heads;
-  const bool level_order = p.num_seqs <= kPfLevelOrderMaxSeqs;
-  auto nblk = [&](int s) {
-    return (level_order && prefix) ? prefix[s]
-                                   : (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem;
-  };
-  int seq = -1, blk = 0;
-  if (level_order) {
-    int max_n = 0;
-    for (int s = 0; s < p.num_seqs; ++s) max_n = max(max_n, nblk(s));
-    auto at_or_above = [&](int r) {   // number of blocks whose index is >= r; decreasing in r
-      int n = 0;
-      for (int s = 0; s < p.num_seqs; ++s) n += max(0, nblk(s) - r);
-      return n;
-    };
-    if (max_n == 0 || t >= at_or_above(0)) return key;
-    int lo = 0, hi = max_n - 1;       // largest r with at_or_above(r) > t
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (at_or_above(mid) > t) lo = mid; else hi = mid - 1;
+  int acc = 0;
+  for (int s = 0; s < p.num_seqs; ++s) {
+    const int n = (cu[s + 1] - cu[s] + kPfRowsPerItem - 1) / kPfRowsPerItem;
+    if (t < acc + n) {
+      key.seq = s;
+      key.q0 = (n - 1 - (t - acc)) * kPfRowsPerItem;
+      key.start = p.q_start ? p.q_start[s] : 0;
+      break;
     }
-    int idx = t - at_or_above(lo + 1);
-    for (int s = 0; s < p.num_seqs; ++s) {
-      if (nblk(s) > lo) {
-        if (idx == 0) {
-          seq = s;
-          break;
-        }
-        --idx;
-      }
-    }
-    blk = lo;
-  } else if (prefix) {
-    int lo = 0, hi = p.num_seqs - 1;   // last sequence whose first block is at or before t
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (prefix[mid] <= t) lo = mid; else hi = mid - 1;
-    }
-    seq = lo;
-    blk = nblk(lo) - 1 - (t - prefix[lo]);
-    if (blk < 0) return key;
-  } else {
-    int acc = 0;
-    for (int s = 0; s < p.num_seqs; ++s) {
-      const int n = nblk(s);
-      if (t < acc + n) {
-        seq = s;
-        blk = n - 1 - (t - acc);      // later blocks of a sequence first
-        break;
-      }
-      acc += n;
-    }
+    acc += n;
   }
-  if (seq < 0) return key;
-  key.seq = seq;
-  key.q0 = blk * kPfRowsPerItem;
-  key.start = p.q_start ? p.q_start[seq] : 0;
   return key;
 }
 
@@ -297,6 +247,26 @@ __device__ __forceinline__ uint32_t prefill_draw_resolve(unsigned long long* wor
       atomicCAS(word, cur, (static_cast<unsigned long long>(tag) << 32) | num_ctas);
   }
   return 0xffffffffu;   // never seen; reads as an end marker
+}
+
+// Bounded mbarrier wait of this kernel.  The kernel has some forty wait sites, and its code size
+// is what its instruction fetch stalls follow, so a site is a probe, a polling loop and two
+// checks; giving up only raises the CTA's abort flag (every later wait of the CTA then returns
+// at once, its results are garbage), and the CTA reports to the diagnostics word once, on its
+// way out.
+__device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
 }
 
 template <int N>
@@ -422,7 +392,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   // abandoned).  The K producer's lane 0 wrote the entry, fully expanded, so that taking it is a
   // wait and three vector loads for everybody else.
   auto take_item = [&](uint32_t n, PrefillItem& it) {
-    mbar_wait(&item_full[n % kPfQueue], (n / kPfQueue) & 1, abort_flag, p.err_word);
+    pf_wait(&item_full[n % kPfQueue], (n / kPfQueue) & 1, abort_flag);
     if (*abort_flag) return false;
     const uint4* src = reinterpret_cast<const uint4*>(&item_q[n % kPfQueue]);
     uint4* dst = reinterpret_cast<uint4*>(&it);
@@ -493,7 +463,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       bool more = !is_v && lane == 0;
       unsigned long long drawn = 0;
       const bool use_tab = cu_cached && p.total_items / p.num_q_heads <= kPfBlockTab;
-      const int32_t* prefix = cu_cached ? prefix_smem : nullptr;
       const uint32_t* blk_tab = reinterpret_cast<const uint32_t*>(smem + L::kTabOff);
       auto draw = [&]() {
         if (more) drawn = atomicAdd(p.sched, 1ull);
@@ -515,7 +484,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               key.head = idx % p.num_q_heads;
               key.start = p.q_start ? p.q_start[key.seq] : 0;
             } else {
-              key = prefill_find_item(p, cu, prefix, idx);
+              key = prefill_find_item(p, cu, idx);
             }
           }
           PrefillItem full;
@@ -535,7 +504,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ip = item_n & 1;
           // the Q buffer is free once every QK of the item two back has retired
           PF_TRACE_BEGIN();
-          mbar_wait(&q_empty[ip], ((item_n >> 1) & 1) ^ 1, abort_flag, p.err_word);
+          pf_wait(&q_empty[ip], ((item_n >> 1) & 1) ^ 1, abort_flag);
           PF_TRACE_END(0);
           if (lane == 0) {
             mbar_arrive_expect_tx(&q_full[ip], L::kTileBytes);
@@ -555,7 +524,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (t >= static_cast<uint32_t>(kRing)) {     // the slot held tile t - kRing
             const uint32_t u = t - kRing;
             PF_TRACE_BEGIN();
-            mbar_wait(&retired[u % 3u], (u / 3u) & 1, abort_flag, p.err_word);
+            pf_wait(&retired[u % 3u], (u / 3u) & 1, abort_flag);
             PF_TRACE_END(1);
           }
           PF_TL(is_v ? 14 : 13, t)
@@ -630,7 +599,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int ip = item_no & 1;
         if (!is_pv) {
           PF_TRACE_BEGIN();
-          mbar_wait(&q_full[ip], (item_no >> 1) & 1, abort_flag, p.err_word);
+          pf_wait(&q_full[ip], (item_no >> 1) & 1, abort_flag);
           PF_TRACE_END(0);
           PF_TLI(4, item_no)
         }
@@ -642,12 +611,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!is_pv) {
             // ---- S_b = Q K_t^T
             PF_TRACE_BEGIN();
-            mbar_wait(&k_full[slot], (t / kRing) & 1, abort_flag, p.err_word);
+            pf_wait(&k_full[slot], (t / kRing) & 1, abort_flag);
             PF_TRACE_END(1);
             PF_TL(0, t)
             if (t >= 3) {     // S_b still holds P of tile t-3 until its PV has retired
               PF_TRACE_BEGIN();
-              mbar_wait(&pv_done[b], ((t - 3) / 3u) & 1, abort_flag, p.err_word);
+              pf_wait(&pv_done[b], ((t - 3) / 3u) & 1, abort_flag);
               PF_TRACE_END(2);
             }
             PF_TL(1, t)
@@ -669,7 +638,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             // ---- O (+)= P_t V_t
             uint8_t* vt = v_ring + slot * L::kTileBytes;
             PF_TRACE_BEGIN();
-            mbar_wait(&v_full[slot], (t / kRing) & 1, abort_flag, p.err_word);
+            pf_wait(&v_full[slot], (t / kRing) & 1, abort_flag);
             PF_TRACE_END(1);
             PF_TL(3, t)
             if (j == n - 1) {
@@ -687,12 +656,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               }
             }
             PF_TRACE_BEGIN();
-            mbar_wait(&p_full[b], (t / 3u) & 1, abort_flag, p.err_word);
+            pf_wait(&p_full[b], (t / 3u) & 1, abort_flag);
             PF_TRACE_END(3);
             PF_TL(4, t)
             if (j == 0) {   // O of the item before must have been read out before it is overwritten
               PF_TRACE_BEGIN();
-              mbar_wait(o_empty, (item_no & 1) ^ 1, abort_flag, p.err_word);
+              pf_wait(o_empty, (item_no & 1) ^ 1, abort_flag);
               PF_TRACE_END(4);
             }
             PF_TL(5, t)
@@ -748,7 +717,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t s_addr = tmem_base + b * kPfN + lane_addr;
         const int j = it.j0 + jr;                        // absolute KV tile
         PF_TRACE_BEGIN();
-        mbar_wait(&s_full[b], (t / 3u) & 1, abort_flag, p.err_word);
+        pf_wait(&s_full[b], (t / 3u) & 1, abort_flag);
         PF_TRACE_END(0);
 #ifdef B200ATTN_PF_TRACE
         const long long tr_tile = clock64();
@@ -756,7 +725,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #endif
         tc_fence_after_sync();
 #ifdef B200ATTN_PF_NOSOFTMAX
-        if (t > 0) mbar_wait(&m_ready[w ^ 1u], (((t + 1) >> 1) - 1) & 1, abort_flag, p.err_word);
+        if (t > 0) pf_wait(&m_ready[w ^ 1u], (((t + 1) >> 1) - 1) & 1, abort_flag);
         mbar_arrive(&m_ready[w]);
         tc_fence_before_sync();
         mbar_arrive(&p_full[b]);
@@ -821,7 +790,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (t > 0) {
           const uint32_t other = (t + 1) >> 1;           // tiles of the other parity before t
           PF_TRACE_BEGIN();
-          mbar_wait(&m_ready[w ^ 1u], (other - 1) & 1, abort_flag, p.err_word);
+          pf_wait(&m_ready[w ^ 1u], (other - 1) & 1, abort_flag);
           PF_TRACE_END(1);
           if (jr > 0) m_prev = m_sh[(w ^ 1u) * kPfM + row];
         }
@@ -882,7 +851,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         // O row rescale (rare: only when the running max moved by more than the threshold):
         // every PV up to the tile before must have retired; PV of this tile waits for p_full.
         if (__any_sync(0xffffffffu, rescale)) {
-          mbar_wait(&pv_done[(t - 1) % 3u], ((t - 1) / 3u) & 1, abort_flag, p.err_word);
+          pf_wait(&pv_done[(t - 1) % 3u], ((t - 1) / 3u) & 1, abort_flag);
           tc_fence_after_sync();
           const float corr =
               !rescale ? 1.f : ((WIN && m_prev == -INFINITY) ? 0.f : fast_exp2(m_prev - m_new));
@@ -913,7 +882,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       // ---- item end: hand this group's (max, sum) of the row to the epilogue
       PF_TRACE_BEGIN();
-      mbar_wait(&stat_empty[ip], ((item_no >> 1) & 1) ^ 1, abort_flag, p.err_word);
+      pf_wait(&stat_empty[ip], ((item_no >> 1) & 1) ^ 1, abort_flag);
       PF_TRACE_END(2);
       stat_sh[(ip * 2 + w) * kPfM + row] = make_float2(m_last, l_run);
       mbar_arrive(&stat_full[ip]);
@@ -943,7 +912,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       t_end += it.n_tiles;
       const uint32_t o_addr = tmem_base + 3 * kPfN + lane_addr;
       PF_TRACE_BEGIN();
-      mbar_wait(&stat_full[ip], ph, abort_flag, p.err_word);
+      pf_wait(&stat_full[ip], ph, abort_flag);
       PF_TRACE_END(0);
       if ((warp & 3) == 0) { PF_TLI(5, item_no) }
       const float2 s0 = stat_sh[(ip * 2 + 0) * kPfM + row];
@@ -955,7 +924,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                       (s1.x == -INFINITY ? 0.f : s1.y * fast_exp2(s1.x - m_fin));
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       PF_TRACE_BEGIN();      // the PV of the item's last tile
-      mbar_wait(&pv_done[(t_end - 1) % 3u], ((t_end - 1) / 3u) & 1, abort_flag, p.err_word);
+      pf_wait(&pv_done[(t_end - 1) % 3u], ((t_end - 1) / 3u) & 1, abort_flag);
       PF_TRACE_END(1);
 #ifdef B200ATTN_PF_TRACE
       const long long tr_ep = clock64();
@@ -1006,6 +975,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+  if (threadIdx.x == 0 && *abort_flag) report_wait_timeout(p.err_word);
 }
 
 }  // namespace b200attn
