@@ -856,7 +856,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           const float corr =
               !rescale ? 1.f : ((WIN && m_prev == -INFINITY) ? 0.f : fast_exp2(m_prev - m_new));
           const uint64_t f2 = pack_f32x2(corr, corr);
-#pragma unroll
+#pragma unroll 1   // rare path: keep it small
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t oreg[32];
             tmem_ld_32x32(o_addr + c * 32, oreg);
@@ -935,7 +935,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           p.out + static_cast<int64_t>(it.seq_q_begin + it.q0 + row) * p.out_row_stride +
           static_cast<int64_t>(it.head) * HD;
       const bool store = row < it.rows_valid;
-#pragma unroll
+#pragma unroll 1   // once per item: small code matters more than the unrolled form's few cycles
       for (int c = 0; c < HD / 16; ++c) {
         uint32_t oreg[16];
         tmem_ld_32x16(o_addr + c * 16, oreg);
