@@ -307,11 +307,11 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
                       : launch_prefill_win<HD, BS, false>(tq, tk, tv, p, sm_count, s);
 }
 
-template <int NB, int S>
+template <int NB, int S, int W>
 static int launch_rowlinear(const CUtensorMap& tw, const CUtensorMap& tx, const RowLinearParams& p,
                             int tiles, cudaStream_t s) {
   using L = RowLinearSmem<NB>;
-  auto kern = rowlinear_allreduce_kernel<NB, S>;
+  auto kern = rowlinear_allreduce_kernel<NB, S, W>;
   static bool smem_allowed[kMaxDevices] = {};
   cudaError_t e = allow_dynamic_smem(kern, L::kTotalBytes, smem_allowed);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -354,15 +354,24 @@ static int launch_rowlinear(const CUtensorMap& tw, const CUtensorMap& tx, const 
   return static_cast<int>(e);
 }
 
+template <int NB, int W>
+static int launch_rowlinear_w(int split, const CUtensorMap& tw, const CUtensorMap& tx,
+                              const RowLinearParams& p, int tiles, cudaStream_t s) {
+  switch (split) {
+    case 8: return launch_rowlinear<NB, 8, W>(tw, tx, p, tiles, s);
+    case 4: return launch_rowlinear<NB, 4, W>(tw, tx, p, tiles, s);
+    case 2: return launch_rowlinear<NB, 2, W>(tw, tx, p, tiles, s);
+    default: return launch_rowlinear<NB, 1, W>(tw, tx, p, tiles, s);
+  }
+}
+
+// the instantiation whose source-rank loops are the shortest that cover the call's world size
 template <int NB>
 static int launch_rowlinear_nb(int split, const CUtensorMap& tw, const CUtensorMap& tx,
                                const RowLinearParams& p, int tiles, cudaStream_t s) {
-  switch (split) {
-    case 8: return launch_rowlinear<NB, 8>(tw, tx, p, tiles, s);
-    case 4: return launch_rowlinear<NB, 4>(tw, tx, p, tiles, s);
-    case 2: return launch_rowlinear<NB, 2>(tw, tx, p, tiles, s);
-    default: return launch_rowlinear<NB, 1>(tw, tx, p, tiles, s);
-  }
+  if (p.world <= 2) return launch_rowlinear_w<NB, 2>(split, tw, tx, p, tiles, s);
+  if (p.world <= 4) return launch_rowlinear_w<NB, 4>(split, tw, tx, p, tiles, s);
+  return launch_rowlinear_w<NB, 8>(split, tw, tx, p, tiles, s);
 }
 
 }  // namespace b200attn

@@ -144,7 +144,10 @@ __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
 // NB: token rows of the MMA (32 / 64 / 128).  S: CTAs per cluster = K splits (1 / 2 / 4 / 8).
-template <int NB, int S>
+// W: bound of the loops over source ranks (2 / 4 / 8 >= world).  The exchange is straight-line
+// code unrolled over sources x units that every CTA runs once, out of a cold instruction cache:
+// with the loops bounded at 8 sources a two-rank call spent a microsecond more fetching it.
+template <int NB, int S, int W>
 __global__ void __launch_bounds__(kRlThreads, 1)
 rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
                            const __grid_constant__ CUtensorMap tm_x, const RowLinearParams p) {
@@ -354,11 +357,11 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
       bool gave_up = !active;
 #pragma unroll
       for (int c = 0; c < kPairs; c += kChunk) {
-        uint2 got[kRlMaxWorld][kChunk];
+        uint2 got[W][kChunk];
         // wanted: the partial of every peer when this CTA reduces, else the owner's result
         // (kept in row 0)
 #pragma unroll
-        for (int src = 0; src < kRlMaxWorld; ++src)
+        for (int src = 0; src < W; ++src)
 #pragma unroll
           for (int u = 0; u < kChunk; ++u) {
             const bool from_src = i_reduce ? (src < p.world && src != p.rank) : (src == 0);
@@ -371,7 +374,7 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
         uint64_t t0 = 0;
         for (uint32_t round = 1;; ++round) {
 #pragma unroll
-          for (int src = 0; src < kRlMaxWorld; ++src) {
+          for (int src = 0; src < W; ++src) {
             if (i_reduce ? src < p.world : src == 0) {
               const uint2* from =
                   rl_unit(own, p, parity, i_reduce ? src : result_area, slot, kPairs, c, col);
@@ -382,7 +385,7 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
           }
           bool pending = false;
 #pragma unroll
-          for (int src = 0; src < kRlMaxWorld; ++src)
+          for (int src = 0; src < W; ++src)
 #pragma unroll
             for (int u = 0; u < kChunk; ++u) pending = pending || got[src][u].y != epoch;
           if (!pending) break;
@@ -412,7 +415,7 @@ rowlinear_allreduce_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (i_reduce) {
               float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-              for (int src = 0; src < kRlMaxWorld; ++src) {
+              for (int src = 0; src < W; ++src) {
                 if (src < p.world) {
                   const uint32_t v = (src == p.rank) ? mine[c + u] : got[src][u].x;
                   a0 += bf16_lo(v);
