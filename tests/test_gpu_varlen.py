@@ -152,3 +152,33 @@ def test_more_sequences_than_the_shared_memory_cache_holds(clean_error_word):
         want = restate.sdpa(q[a:b].transpose(0, 1)[None].float(), k[a:b].transpose(0, 1)[None].float(),
                             v[a:b].transpose(0, 1)[None].float(), True, hd ** -0.5)[0].transpose(0, 1)
         assert_attention_close(out[a:b], want, f"seq {i}")
+
+
+def test_a_list_too_long_to_tabulate_is_searched(clean_error_word):
+    """More 128-row blocks than the kernel tabulates (1024): the drawing thread finds each item
+    by a scan of cu_q instead.  Three sequences, 1040 blocks in all; rows at the start, around
+    a sequence boundary and at the very end are compared with fp32 attention computed by torch
+    over the same bf16 inputs."""
+    from b200attn import ops
+
+    nq, nkv, hd = 2, 1, 64
+    lens = [70000, 128 * 3 + 5, 62000]
+    assert sum((n + 127) // 128 for n in lens) > 1024
+    cu_q = torch.tensor([0, lens[0], lens[0] + lens[1], sum(lens)], dtype=torch.int32)
+    total = int(cu_q[-1])
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(total, nq, hd, generator=g, device="cuda").bfloat16()
+    k = torch.randn(total, nkv, hd, generator=g, device="cuda").bfloat16()
+    v = torch.randn(total, nkv, hd, generator=g, device="cuda").bfloat16()
+    out = ops.prefill(q, k, v, cu_q, scale=hd ** -0.5)
+    assert ops.read_error_word() == 0
+    for s, (lo, n) in enumerate(zip(cu_q[:-1].tolist(), lens)):
+        rows = sorted({0, 1, 127, 128, n // 2, n - 2, n - 1})
+        for h in range(nq):
+            qs = q[lo:lo + n, h].float()[rows]                      # [r, hd]
+            ks, vs = k[lo:lo + n, 0].float(), v[lo:lo + n, 0].float()
+            sc = (qs @ ks.t()) * hd ** -0.5
+            pos = torch.tensor(rows, device="cuda")[:, None]
+            sc = sc.masked_fill(torch.arange(n, device="cuda")[None, :] > pos, float("-inf"))
+            want = torch.softmax(sc, -1) @ vs
+            assert_attention_close(out[lo:lo + n, h][rows], want, f"sequence {s} head {h}")
