@@ -44,7 +44,7 @@ def test_decode_golden(name, clean_error_word):
 
 @pytest.mark.parametrize("splits", [0, 1, 2, 3, 7])
 def test_config1_all_split_counts(splits, clean_error_word):
-    """BASELINE config 1: nq 32 / nkv 8 / hd 64 / bs 32, 8 users, contexts U[128,1024]."""
+    """benchmark config 1: nq 32 / nkv 8 / hd 64 / bs 32, 8 users, contexts U[128,1024]."""
     case = config1()
     assert_attention_close(run_decode(case, splits), oracle_decode(case), f"splits={splits}")
 

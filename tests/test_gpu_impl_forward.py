@@ -72,7 +72,7 @@ def test_impl_chunk_golden(clean_error_word):
 
 
 def test_impl_decode_config1(clean_error_word):
-    """BASELINE config 1 end to end through forward: scatter bit-exact, attention in budget."""
+    """benchmark config 1 end to end through forward: scatter bit-exact, attention in budget."""
     from b200attn import B200Metadata
 
     case = config1()

@@ -124,7 +124,7 @@ def test_varlen_ragged_lengths_and_starts(clean_error_word):
 
 
 def test_paged_and_fresh_forms_agree_at_config2_shape(clean_error_word):
-    """BASELINE config 2 geometry (nq 32, nkv 8, hd 128, bs 64, T 2048) on one sequence: the
+    """benchmark config 2 geometry (nq 32, nkv 8, hd 128, bs 64, T 2048) on one sequence: the
     paged form with chunk_start 0 and the fresh-KV form give the same bits, and rows are
     checked against the oracle on a strided subset of heads."""
     from b200attn import ops

@@ -1,5 +1,5 @@
 """vLLM varlen form through forward(): decode rows and prefill / chunk rows in one batch (the
-shape of BASELINE config 3, scaled to sizes the oracle finishes in seconds).  The reference never
+shape of benchmark config 3, scaled to sizes the oracle finishes in seconds).  The reference never
 mixes the two in one pass (its scheduler runs prefill first, ascend_scheduler.py:486-489), so the
 expected result is the concatenation of its two passes: the decode op over the decode rows and
 the chunked op over the chunk rows.  Cache writes bit-exact, outputs within the bf16 budget."""

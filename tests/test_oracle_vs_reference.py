@@ -60,7 +60,7 @@ def test_one_token_remainder_chunk():
 
 
 def test_config1_decode_step_live():
-    """BASELINE config 1 through the live reference ops (GQA via the per-group loop) vs the oracle:
+    """benchmark config 1 through the live reference ops (GQA via the per-group loop) vs the oracle:
     cache writes bit-exact, attention equal in fp32 and in native bf16."""
     c = config1()
     users = c.users
