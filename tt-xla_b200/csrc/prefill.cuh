@@ -42,6 +42,10 @@
 // compare-and-swap, and the CTA that draws the last end marker puts the word back to zero (so
 // that a replay of a captured launch, which carries the same tag, starts afresh).
 // Every mbarrier wait is bounded; tensor memory is always freed before exit.
+// Code size is a first-order cost here: four roles run different code on every SM
+// sub-partition, and whatever runs once per item (mask, epilogue, taking an item) runs out of a
+// cold instruction cache.  Hence the compact wait (pf_wait), the rolled rare loops, and the item
+// order tabulated once instead of searched per item.
 #pragma once
 #include "ptx.cuh"
 
