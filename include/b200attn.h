@@ -352,6 +352,12 @@ int b200attn_dequant_pages_fp8(void* k_dst, void* v_dst, const void* k_cache, co
  *   kv_is_paged = 1: k_src / v_src are the K and V caches; page_table[s, :] lists sequence
  *                    s's blocks in logical order (prefix + chunk already written).
  * cu_q_host mirrors cu_q on the host (the launch grid is sized from it).
+ * The CTAs of a launch share out its work through a counter word inside the library (64 words
+ * per device, handed to launches in turn and tagged per call, so launches on different streams
+ * do not meet).  A launch captured into a CUDA graph keeps its word and tag: replay it as often
+ * as needed, but never let two replays of the SAME captured launch run at the same time (two
+ * streams replaying one graph), and read the diagnostics word (b200attn_read_error_word, which
+ * also clears the counters) after a launch that reported a timeout before replaying it.
  * ------------------------------------------------------------------------------------------ */
 int b200attn_prefill(void* out, int64_t out_row_stride,
                      const void* q, int64_t q_row_stride,
