@@ -619,7 +619,11 @@ int b200attn_decode_auto_splits(int num_users, int num_kv_heads, int head_size,
   const double tile_bytes = 2.0 * kDecTile * head_size * 2.0;
   const double bw = 7.0e6;                                   // bytes per us
   const int occ = head_size > 64 ? 2 : 3;                    // resident CTAs per SM
-  const double t_alone = 0.54 * tile_bytes / 32768.0;
+  // ... but never faster than ~0.45 us per tile: below 32 KiB a tile's time is the round trip of
+  // its loads and barriers, not its bytes (head_size 64: 13.3 us with one split against 10.2 us
+  // with four on eight users of up to 1024 tokens)
+  const double t_bytes = 0.54 * tile_bytes / 32768.0;
+  const double t_alone = t_bytes > 0.45 ? t_bytes : 0.45;
   const int64_t tiles = (max_context_len + kDecTile - 1) / kDecTile;
   const int64_t base = static_cast<int64_t>(num_users) * num_kv_heads;
   const double slots = static_cast<double>(occ) * sm;
